@@ -1,0 +1,147 @@
+/*
+ * relax_b200 - C ABI of the B200 (sm_100a) weight-only dequantize-matmul library.
+ *
+ * Every entry point takes plain pointers and sizes, returns 0 on success and -1 on failure
+ * (the message is then available from rb200_last_error(), thread local), never aborts the
+ * process and never falls back to a CPU path.  Device pointers must belong to the CUDA
+ * device that is current on the calling thread; `stream` is a cudaStream_t passed as void*.
+ *
+ * Each declaration names the interface of the reference project (mlc-ai/relax, paths inside
+ * that project) that it stands in for.
+ */
+#ifndef RELAX_B200_H_
+#define RELAX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RB200_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------ errors, streams */
+
+/* Mirrors TVMGetLastError (include/tvm/runtime/c_runtime_api.h:245). */
+RB200_API const char* rb200_last_error(void);
+
+/*
+ * The stream later PackedFunc-style calls on this thread launch on; stands in for the
+ * "runtime.get_cuda_stream" lookup the generated host code performs
+ * (python/tvm/contrib/cutlass/gemm_operation.py:432-434, src/runtime/cuda/cuda_device_api.cc:318-320)
+ * and for TVMSetStream (c_runtime_api.h).  Plain C entry points take the stream explicitly.
+ */
+RB200_API int rb200_set_stream(void* stream);
+RB200_API void* rb200_get_stream(void);
+
+/*
+ * Reads (and clears) the device-side status word that bounded waits inside the kernels set
+ * when they give up.  Synchronises the given stream.  0 = no error recorded.
+ */
+RB200_API int rb200_check_async_error(void* stream, int* status_out);
+
+/* ------------------------------------------------------------------ weight preprocess */
+
+/* Source layouts accepted by rb200_preprocess_weight. */
+#define RB200_LAYOUT_FT_KN 0 /* int8 container [K, N/2] (int4, low nibble = even column) or [K, N] (int8), signed codes */
+#define RB200_LAYOUT_Q4_NK 1 /* uint32 [N, K/8], nibble j of a word = element 8*word + j, unsigned codes */
+
+/*
+ * Repack a packed int4/int8 weight into the kernel-private fragment layout; the result has
+ * exactly the byte size of the source.  Stands in for
+ *   cutlass.ft_preprocess_weight(NDArray packed_weight, int sm, bool is_int4)
+ *   (src/runtime/contrib/cutlass/weight_preprocess.cc:38-58), which calls
+ *   fastertransformer::preprocess_weights(out, in, num_experts, rows, cols, is_int4, sm).
+ * `k` and `n` are the logical (unpacked) reduction and output extents of ONE expert; both
+ * buffers are device memory, `dst` must not alias `src`.  Signed FT codes are stored biased
+ * to unsigned (int4: +8, int8: +128), as the reference's preprocess does.
+ * Requirements: n % 16 == 0; k % 64 == 0 (int4) or k % 32 == 0 (int8).
+ */
+RB200_API int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int64_t k,
+                                      int64_t n, int is_int4, int src_layout, void* stream);
+
+/* ------------------------------------------------------------------ dequantize-matmul */
+
+#define RB200_ACT_IDENTITY 0
+#define RB200_ACT_RELU 1
+#define RB200_ACT_SILU 2
+#define RB200_ACT_GELU 3
+#define RB200_BIN_NONE 0
+#define RB200_BIN_PLUS 1
+#define RB200_BIN_MULTIPLY 2
+#define RB200_UN_IDENTITY 0
+#define RB200_UN_RELU 1
+
+/*
+ * Full description of one  out = unary(binary(act(x @ dequant(W)^T + bias), residual))  call.
+ *   dequant:  wq[n,k] = f16_rn((f16(u[n,k]) - z) * s),  s = scales[n*scale_stride_n + (k/group)*scale_stride_g],
+ *             z = zeros[same index] when zeros != NULL, else the constant `zero_const`.
+ *   matmul :  fp32 accumulation, one rounding to fp16 after the epilogue.
+ */
+typedef struct rb200_gemm_desc {
+  uint32_t struct_size;     /* sizeof(rb200_gemm_desc), for forward compatibility */
+  int32_t weight_bits;      /* 4 or 8 */
+  const void* x;            /* fp16 [m, k], row stride ldx elements */
+  const void* w;            /* preprocessed weight from rb200_preprocess_weight */
+  const void* scales;       /* fp16 */
+  const void* zeros;        /* fp16 per-group zero points, or NULL */
+  const void* bias;         /* fp16 or NULL */
+  const void* residual;     /* fp16 [m, n] or NULL */
+  void* out;                /* fp16 [m, n], row stride ldo elements */
+  int64_t m, n, k;
+  int64_t ldx, ldo;
+  int64_t group_size;       /* <= 0 or >= k: one scale per output channel */
+  int64_t scale_stride_n;   /* elements between consecutive n */
+  int64_t scale_stride_g;   /* elements between consecutive k-groups */
+  int64_t bias_stride;      /* 0: bias[n] broadcast over rows; n: bias[m, n] */
+  float zero_const;         /* used when zeros == NULL (7 q4f16_1, 8 FT int4, 128 FT int8) */
+  int32_t activation;       /* RB200_ACT_* */
+  int32_t binary_op;        /* RB200_BIN_* (needs residual) */
+  int32_t unary_op;         /* RB200_UN_* */
+  int32_t reserved;
+  void* workspace;          /* optional caller scratch (device); NULL -> library-owned per-device scratch */
+  size_t workspace_bytes;
+} rb200_gemm_desc;
+
+/* General entry.  Chooses the decode kernel (m <= 32) or the tensor-core kernel (m > 32). */
+RB200_API int rb200_gemm_fp16_intx(const rb200_gemm_desc* desc, void* stream);
+
+/* Scratch bytes rb200_gemm_fp16_intx may use for this problem on the current device. */
+RB200_API size_t rb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int weight_bits);
+
+/*
+ * Stand-ins for the calls the reference's generated host code makes
+ * (python/tvm/contrib/cutlass/gemm_operation.py:441-447 and :449-458):
+ *   fastertransformer::gemm_fp16_int_bias_act<WeightT, QuantOp>(A, B, scales, bias, out, act,
+ *        m, n, k, group_size, bias_stride, workspace, workspace_bytes, stream)
+ *   fastertransformer::gemm_fp16_int_bias_act_residual<WeightT, QuantOp>(A, B, scales, bias,
+ *        residual, out, act, binary_op, unary_op, m, n, k, group_size, workspace, bytes, stream)
+ * WeightT becomes `weight_bits`; QuantOp follows from group_size (== k or <= 0: per column
+ * scales [n]; otherwise fine-grained scales [k/group_size, n]).  B comes from
+ * rb200_preprocess_weight(..., RB200_LAYOUT_FT_KN).  Activation / op names as the reference
+ * passes them: "identity"|"relu"|"silu"|"gelu", "plus"|"multiply", "identity"|"relu".
+ */
+RB200_API int rb200_gemm_fp16_int_bias_act(const void* A, const void* B, const void* scales,
+                                           const void* bias, void* out, const char* activation,
+                                           int m, int n, int k, int group_size, int bias_stride,
+                                           int weight_bits, void* workspace,
+                                           size_t workspace_bytes, void* stream);
+RB200_API int rb200_gemm_fp16_int_bias_act_residual(
+    const void* A, const void* B, const void* scales, const void* bias, const void* residual,
+    void* out, const char* activation, const char* binary_op, const char* unary_op, int m, int n,
+    int k, int group_size, int weight_bits, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Debug/verification entry: writes the dequantised weight wq fp16 [n, k] (row-major) that the
+ * matmul kernels feed to the tensor cores, produced by the same device decode routine.  Uses
+ * the w / scales / zeros / group / stride / zero_const fields of the descriptor.  The arithmetic
+ * it exposes is the reference's decode TIR (tests/python/dlight/test_gpu_gemv.py:193-198,
+ * tests/python/relax/test_codegen_cutlass.py:1371-1389, :1628, :2041).
+ */
+RB200_API int rb200_dequantize(const rb200_gemm_desc* desc, void* wq_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RELAX_B200_H_ */

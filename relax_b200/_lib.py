@@ -1,0 +1,111 @@
+"""ctypes bindings of ``librelax_b200.so`` (the C ABI declared in ``include/relax_b200*.h``).
+
+There is no fallback: if the shared library is missing or fails to load, importing this module
+raises, and so does every operator of the package.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "librelax_b200.so")
+
+
+class GemmDesc(ctypes.Structure):
+    """``rb200_gemm_desc`` of include/relax_b200.h."""
+
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32), ("weight_bits", ctypes.c_int32),
+        ("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+        ("zeros", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+        ("out", ctypes.c_void_p),
+        ("m", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64),
+        ("ldx", ctypes.c_int64), ("ldo", ctypes.c_int64),
+        ("group_size", ctypes.c_int64), ("scale_stride_n", ctypes.c_int64),
+        ("scale_stride_g", ctypes.c_int64), ("bias_stride", ctypes.c_int64),
+        ("zero_const", ctypes.c_float),
+        ("activation", ctypes.c_int32), ("binary_op", ctypes.c_int32), ("unary_op", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
+class DLDevice(ctypes.Structure):
+    _fields_ = [("device_type", ctypes.c_int32), ("device_id", ctypes.c_int32)]
+
+
+class DLDataType(ctypes.Structure):
+    _fields_ = [("code", ctypes.c_uint8), ("bits", ctypes.c_uint8), ("lanes", ctypes.c_uint16)]
+
+
+class DLTensor(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p), ("device", DLDevice), ("ndim", ctypes.c_int32),
+        ("dtype", DLDataType), ("shape", ctypes.POINTER(ctypes.c_int64)),
+        ("strides", ctypes.POINTER(ctypes.c_int64)), ("byte_offset", ctypes.c_uint64),
+    ]
+
+
+class Value(ctypes.Union):
+    """``RB200Value`` (layout of the reference's TVMValue)."""
+
+    _fields_ = [("v_int64", ctypes.c_int64), ("v_float64", ctypes.c_double),
+                ("v_handle", ctypes.c_void_p), ("v_str", ctypes.c_char_p)]
+
+
+ARG_INT, ARG_FLOAT, ARG_HANDLE, ARG_NULL, ARG_DLTENSOR, ARG_STR = 0, 2, 3, 4, 7, 11
+
+# every symbol the headers declare, with (restype, argtypes)
+_V = ctypes.c_void_p
+_I = ctypes.c_int
+_I64 = ctypes.c_int64
+_S = ctypes.c_char_p
+SIGNATURES = {
+    "rb200_last_error": (_S, []),
+    "rb200_set_stream": (_I, [_V]),
+    "rb200_get_stream": (_V, []),
+    "rb200_check_async_error": (_I, [_V, ctypes.POINTER(_I)]),
+    "rb200_preprocess_weight": (_I, [_V, _V, _I64, _I64, _I64, _I, _I, _V]),
+    "rb200_gemm_fp16_intx": (_I, [ctypes.POINTER(GemmDesc), _V]),
+    "rb200_gemm_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64, _I]),
+    "rb200_gemm_fp16_int_bias_act": (_I, [_V, _V, _V, _V, _V, _S, _I, _I, _I, _I, _I, _I, _V,
+                                          ctypes.c_size_t, _V]),
+    "rb200_gemm_fp16_int_bias_act_residual": (_I, [_V, _V, _V, _V, _V, _V, _S, _S, _S, _I, _I, _I,
+                                                   _I, _I, _V, ctypes.c_size_t, _V]),
+    "rb200_dequantize": (_I, [ctypes.POINTER(GemmDesc), _V, _V]),
+    "RB200FuncGetGlobal": (_I, [_S, ctypes.POINTER(_V)]),
+    "RB200FuncCall": (_I, [_V, ctypes.POINTER(Value), ctypes.POINTER(_I), _I,
+                           ctypes.POINTER(Value), ctypes.POINTER(_I)]),
+    "RB200FuncRegisterGlobal": (_I, [_S, _V, _V, _I]),
+    "RB200FuncListGlobalNames": (_I, [ctypes.POINTER(_I), ctypes.POINTER(ctypes.POINTER(_S))]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            "relax_b200: %s is missing - build it with `python -m relax_b200.build`; there is no "
+            "fallback path" % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+class RB200Error(RuntimeError):
+    pass
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = load().rb200_last_error()
+        raise RB200Error(msg.decode() if msg else "relax_b200 call failed")

@@ -1,0 +1,486 @@
+// PackedFunc-style registry and the operator shims registered in it.  Host C++ only: every
+// shim unpacks DLTensor arguments, validates them, and calls the plain C ABI of relax_b200.h.
+//
+// Mirrors: global registry (src/runtime/registry.cc, include/tvm/runtime/c_runtime_api.h:385-486),
+// the packed wrapper the reference's C-source codegen emits around each offloaded operator
+// (src/relay/backend/contrib/codegen_c/codegen_c.h:100-131,163-235), and the contrib function
+// src/runtime/contrib/cutlass/weight_preprocess.cc:38-58.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/relax_b200_packed.h"
+
+namespace rb200 {
+void set_last_error(const char* fmt, ...);
+}
+
+namespace {
+
+struct Entry {
+  RB200PackedCFunc fn;
+  void* resource;
+  std::string name;
+};
+
+std::mutex& reg_mutex() {
+  static std::mutex m;
+  return m;
+}
+std::map<std::string, Entry*>& registry() {
+  static std::map<std::string, Entry*> r;
+  return r;
+}
+
+#define PF_CHECK(cond, ...)               \
+  do {                                    \
+    if (!(cond)) {                        \
+      rb200::set_last_error(__VA_ARGS__); \
+      return -1;                          \
+    }                                     \
+  } while (0)
+
+struct Args {
+  RB200Value* v;
+  int* tc;
+  int n;
+  const char* fname;
+
+  bool is_null(int i) const { return tc[i] == (int)RB200_ARG_NULL || (is_tensor_code(i) && v[i].v_handle == nullptr); }
+  bool is_tensor_code(int i) const {
+    return tc[i] == (int)RB200_ARG_DLTENSOR || tc[i] == (int)RB200_ARG_NDARRAY;
+  }
+  int tensor(int i, const DLTensor** out, bool optional = false) const {
+    *out = nullptr;
+    PF_CHECK(i < n, "%s: missing argument %d", fname, i);
+    if (optional && is_null(i)) return 0;
+    PF_CHECK(is_tensor_code(i) && v[i].v_handle, "%s: argument %d must be a tensor (type code %d)",
+             fname, i, tc[i]);
+    *out = static_cast<const DLTensor*>(v[i].v_handle);
+    return 0;
+  }
+  int integer(int i, int64_t* out) const {
+    PF_CHECK(i < n && tc[i] == (int)RB200_ARG_INT, "%s: argument %d must be an int", fname, i);
+    *out = v[i].v_int64;
+    return 0;
+  }
+  int real(int i, double* out) const {
+    PF_CHECK(i < n && (tc[i] == (int)RB200_ARG_FLOAT || tc[i] == (int)RB200_ARG_INT),
+             "%s: argument %d must be a number", fname, i);
+    *out = tc[i] == (int)RB200_ARG_FLOAT ? v[i].v_float64 : (double)v[i].v_int64;
+    return 0;
+  }
+  int str(int i, const char** out) const {
+    PF_CHECK(i < n && (tc[i] == (int)RB200_ARG_STR || tc[i] == (int)RB200_ARG_NULL),
+             "%s: argument %d must be a string", fname, i);
+    *out = tc[i] == (int)RB200_ARG_STR ? v[i].v_str : "";
+    return 0;
+  }
+};
+
+bool compact(const DLTensor* t) {
+  if (!t->strides) return true;
+  int64_t expect = 1;
+  for (int i = t->ndim - 1; i >= 0; --i) {
+    if (t->shape[i] != 1 && t->strides[i] != expect) return false;
+    expect *= t->shape[i];
+  }
+  return true;
+}
+void* data_of(const DLTensor* t) { return static_cast<char*>(t->data) + t->byte_offset; }
+int64_t numel(const DLTensor* t) {
+  int64_t n = 1;
+  for (int i = 0; i < t->ndim; ++i) n *= t->shape[i];
+  return n;
+}
+bool is_dtype(const DLTensor* t, int code, int bits) {
+  return t->dtype.code == code && t->dtype.bits == bits && t->dtype.lanes == 1;
+}
+
+int check_tensor(const char* fn, const char* what, const DLTensor* t, int code, int bits,
+                 bool need_cuda = true) {
+  PF_CHECK(is_dtype(t, code, bits), "%s: %s has dtype (code %d, bits %d), expected (code %d, bits %d)",
+           fn, what, t->dtype.code, t->dtype.bits, code, bits);
+  PF_CHECK(compact(t), "%s: %s must be compact row-major", fn, what);
+  if (need_cuda) {
+    PF_CHECK(t->device.device_type == kDLCUDA, "%s: %s must live on a CUDA device (device type %d)",
+             fn, what, (int)t->device.device_type);
+    int dev = -1;
+    cudaGetDevice(&dev);
+    PF_CHECK(dev == t->device.device_id, "%s: %s is on cuda:%d but the current device is cuda:%d", fn,
+             what, t->device.device_id, dev);
+  }
+  return 0;
+}
+bool is_f16(const DLTensor* t) { return is_dtype(t, kDLFloat, 16); }
+
+// ------------------------------------------------------------------ preprocess
+int preprocess_common(const char* fn, const DLTensor* w, const DLTensor* out, bool is_int4,
+                      int layout) {
+  PF_CHECK(w->ndim == 2 || w->ndim == 3, "%s: weight must be 2-D or 3-D, got %d-D", fn, w->ndim);
+  PF_CHECK(out->ndim == w->ndim, "%s: out rank differs from input", fn);
+  for (int i = 0; i < w->ndim; ++i)
+    PF_CHECK(out->shape[i] == w->shape[i], "%s: out shape differs from input at dim %d", fn, i);
+  PF_CHECK(out->dtype.code == w->dtype.code && out->dtype.bits == w->dtype.bits,
+           "%s: out dtype differs from input", fn);
+  PF_CHECK(compact(w) && compact(out), "%s: tensors must be compact", fn);
+  PF_CHECK(w->device.device_type == out->device.device_type &&
+               w->device.device_id == out->device.device_id,
+           "%s: out must be on the input's device", fn);
+  const bool is_2d = w->ndim == 2;
+  const int64_t experts = is_2d ? 1 : w->shape[0];
+  const int64_t rows = w->shape[is_2d ? 0 : 1];
+  const int64_t cols = w->shape[is_2d ? 1 : 2];
+  const int64_t elem_bytes = w->dtype.bits / 8;
+  int64_t k, n;
+  if (layout == RB200_LAYOUT_FT_KN) {
+    PF_CHECK(w->dtype.bits == 8 && (w->dtype.code == kDLInt || w->dtype.code == kDLUInt),
+             "%s: FT weights must be int8", fn);
+    k = rows;
+    n = cols * (is_int4 ? 2 : 1);
+  } else {
+    PF_CHECK(is_dtype(w, kDLUInt, 32) || is_dtype(w, kDLInt, 32), "%s: q4f16 weights must be uint32", fn);
+    n = rows;
+    k = cols * 8;
+  }
+  const size_t bytes = (size_t)(experts * rows * cols * elem_bytes);
+  cudaStream_t stream = static_cast<cudaStream_t>(rb200_get_stream());
+  if (w->device.device_type == kDLCUDA) {
+    return rb200_preprocess_weight(data_of(w), data_of(out), experts, k, n, is_int4 ? 1 : 0, layout,
+                                   stream);
+  }
+  PF_CHECK(w->device.device_type == kDLCPU || w->device.device_type == kDLCUDAHost,
+           "%s: unsupported device type %d", fn, (int)w->device.device_type);
+  // Host tensors: the repack itself always runs on the GPU; stage through device memory.
+  void* d_in = nullptr;
+  void* d_out = nullptr;
+  cudaError_t e = cudaMalloc(&d_in, bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&d_out, bytes);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d_in, data_of(w), bytes, cudaMemcpyHostToDevice, stream);
+  int rc = -1;
+  if (e == cudaSuccess) {
+    rc = rb200_preprocess_weight(d_in, d_out, experts, k, n, is_int4 ? 1 : 0, layout, stream);
+    if (rc == 0) {
+      e = cudaMemcpyAsync(data_of(out), d_out, bytes, cudaMemcpyDeviceToHost, stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    }
+  }
+  if (d_in) cudaFree(d_in);
+  if (d_out) cudaFree(d_out);
+  if (e != cudaSuccess) {
+    rb200::set_last_error("%s: staging a host tensor through the device failed: %s", fn,
+                          cudaGetErrorString(e));
+    return -1;
+  }
+  return rc;
+}
+
+int pf_ft_preprocess_weight(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "cutlass.ft_preprocess_weight"};
+  const DLTensor *w, *out;
+  int64_t sm, is_int4;
+  PF_CHECK(n == 4, "%s expects (packed_weight, sm, is_int4, out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &w) || a.integer(1, &sm) || a.integer(2, &is_int4) || a.tensor(3, &out)) return -1;
+  PF_CHECK(sm >= 70 && sm <= 120, "%s: implausible sm=%lld", a.fname, (long long)sm);
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return preprocess_common(a.fname, w, out, is_int4 != 0, RB200_LAYOUT_FT_KN);
+}
+
+int pf_preprocess_q4f16(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "relax_b200.preprocess_weight_q4f16"};
+  const DLTensor *w, *out;
+  PF_CHECK(n == 2, "%s expects (packed_weight, out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &w) || a.tensor(1, &out)) return -1;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return preprocess_common(a.fname, w, out, true, RB200_LAYOUT_Q4_NK);
+}
+
+// ------------------------------------------------------------------ GEMM shims
+int parse_names(const char* fn, const char* act, const char* bin, const char* un, rb200_gemm_desc* d) {
+  struct {
+    const char* s;
+    int v;
+  } acts[] = {{"", 0}, {"identity", 0}, {"relu", 1}, {"silu", 2}, {"gelu", 3}},
+    bins[] = {{"", 0}, {"none", 0}, {"plus", 1}, {"multiply", 2}},
+    uns[] = {{"", 0}, {"identity", 0}, {"relu", 1}};
+  bool ok = false;
+  for (auto& e : acts)
+    if (!strcmp(act, e.s)) d->activation = e.v, ok = true;
+  PF_CHECK(ok, "%s: unknown activation '%s'", fn, act);
+  ok = false;
+  for (auto& e : bins)
+    if (!strcmp(bin, e.s)) d->binary_op = e.v, ok = true;
+  PF_CHECK(ok, "%s: unknown binary_op '%s'", fn, bin);
+  ok = false;
+  for (auto& e : uns)
+    if (!strcmp(un, e.s)) d->unary_op = e.v, ok = true;
+  PF_CHECK(ok, "%s: unknown unary_op '%s'", fn, un);
+  return 0;
+}
+
+int64_t lead_rows(const DLTensor* t) {  // product of all dims but the last
+  int64_t m = 1;
+  for (int i = 0; i + 1 < t->ndim; ++i) m *= t->shape[i];
+  return m;
+}
+
+// (x, w_pre, scales, bias|null, residual|null, activation, binary_op, unary_op, m, n, k,
+//  group_size, bias_stride, out)
+int ft_gemm(const char* fname, int bits, RB200Value* v, int* tc, int n_args, int* ret_tc) {
+  Args a{v, tc, n_args, fname};
+  PF_CHECK(n_args == 14, "%s expects 14 arguments, got %d", fname, n_args);
+  const DLTensor *x, *w, *s, *bias, *res, *out;
+  const char *act, *bin, *un;
+  int64_t m, n, k, group, bias_stride;
+  if (a.tensor(0, &x) || a.tensor(1, &w) || a.tensor(2, &s) || a.tensor(3, &bias, true) ||
+      a.tensor(4, &res, true) || a.str(5, &act) || a.str(6, &bin) || a.str(7, &un) ||
+      a.integer(8, &m) || a.integer(9, &n) || a.integer(10, &k) || a.integer(11, &group) ||
+      a.integer(12, &bias_stride) || a.tensor(13, &out))
+    return -1;
+  if (check_tensor(fname, "x", x, kDLFloat, 16) || check_tensor(fname, "scales", s, kDLFloat, 16) ||
+      check_tensor(fname, "out", out, kDLFloat, 16))
+    return -1;
+  PF_CHECK(w->dtype.bits == 8 && compact(w) && w->device.device_type == kDLCUDA,
+           "%s: weight must be a compact int8 CUDA tensor", fname);
+  PF_CHECK(w->ndim == 2 && w->shape[0] == k && w->shape[1] * (bits == 4 ? 2 : 1) == n,
+           "%s: weight shape [%lld, %lld] does not match k=%lld, n=%lld", fname,
+           (long long)w->shape[0], (long long)(w->ndim > 1 ? w->shape[1] : 0), (long long)k, (long long)n);
+  PF_CHECK(x->ndim >= 1 && x->shape[x->ndim - 1] == k && lead_rows(x) == m,
+           "%s: x shape does not match m=%lld, k=%lld", fname, (long long)m, (long long)k);
+  PF_CHECK(numel(out) == m * n, "%s: out has %lld elements, expected m*n=%lld", fname,
+           (long long)numel(out), (long long)(m * n));
+  const bool per_col = group <= 0 || group >= k;
+  PF_CHECK(numel(s) == (per_col ? n : (k / group) * n), "%s: scales have %lld elements, expected %lld",
+           fname, (long long)numel(s), (long long)(per_col ? n : (k / group) * n));
+  const char* a_name = act;
+  rb200_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  if (parse_names(fname, a_name, bin, un, &d)) return -1;
+  if (bias) {
+    if (check_tensor(fname, "bias", bias, kDLFloat, 16)) return -1;
+    PF_CHECK(numel(bias) == (bias_stride == 0 ? n : m * n), "%s: bias size does not match bias_stride",
+             fname);
+  }
+  if (res) {
+    if (check_tensor(fname, "residual", res, kDLFloat, 16)) return -1;
+    PF_CHECK(numel(res) == m * n, "%s: residual must have m*n elements", fname);
+  }
+  void* stream = rb200_get_stream();
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  if (res) {
+    PF_CHECK(bias_stride == 0, "%s: the residual form takes a row-vector bias (bias_stride 0)", fname);
+    return rb200_gemm_fp16_int_bias_act_residual(
+        data_of(x), data_of(w), data_of(s), bias ? data_of(bias) : nullptr, data_of(res), data_of(out),
+        act, bin[0] ? bin : "plus", un, (int)m, (int)n, (int)k, (int)group, bits, nullptr, 0, stream);
+  }
+  return rb200_gemm_fp16_int_bias_act(data_of(x), data_of(w), data_of(s),
+                                      bias ? data_of(bias) : nullptr, data_of(out), act, (int)m, (int)n,
+                                      (int)k, (int)group, (int)bias_stride, bits, nullptr, 0, stream);
+}
+int pf_ft_gemm_int4(RB200Value* v, int* tc, int n, RB200Value*, int* ret_tc, void*) {
+  return ft_gemm("cutlass.ft_gemm_fp16_int4", 4, v, tc, n, ret_tc);
+}
+int pf_ft_gemm_int8(RB200Value* v, int* tc, int n, RB200Value*, int* ret_tc, void*) {
+  return ft_gemm("cutlass.ft_gemm_fp16_int8", 8, v, tc, n, ret_tc);
+}
+
+// (x, w_pre, scales, zeros|null, bias|null, residual|null, activation, binary_op, unary_op,
+//  group_size, zero_const, out)
+int pf_gemm_q4f16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
+  const char* fname = "relax_b200.gemm_fp16_q4f16";
+  Args a{v, tc, n_args, fname};
+  PF_CHECK(n_args == 12, "%s expects 12 arguments, got %d", fname, n_args);
+  const DLTensor *x, *w, *s, *z, *bias, *res, *out;
+  const char *act, *bin, *un;
+  int64_t group;
+  double zconst;
+  if (a.tensor(0, &x) || a.tensor(1, &w) || a.tensor(2, &s) || a.tensor(3, &z, true) ||
+      a.tensor(4, &bias, true) || a.tensor(5, &res, true) || a.str(6, &act) || a.str(7, &bin) ||
+      a.str(8, &un) || a.integer(9, &group) || a.real(10, &zconst) || a.tensor(11, &out))
+    return -1;
+  if (check_tensor(fname, "x", x, kDLFloat, 16) || check_tensor(fname, "scales", s, kDLFloat, 16) ||
+      check_tensor(fname, "out", out, kDLFloat, 16))
+    return -1;
+  PF_CHECK(w->ndim == 2 && w->dtype.bits == 32 && compact(w) && w->device.device_type == kDLCUDA,
+           "%s: weight must be a compact uint32 [N, K/8] CUDA tensor", fname);
+  const int64_t n = w->shape[0], k = w->shape[1] * 8;
+  PF_CHECK(x->ndim >= 1 && x->shape[x->ndim - 1] == k, "%s: x inner extent %lld != k=%lld", fname,
+           (long long)x->shape[x->ndim - 1], (long long)k);
+  const int64_t m = lead_rows(x);
+  PF_CHECK(numel(out) == m * n, "%s: out has %lld elements, expected %lld", fname,
+           (long long)numel(out), (long long)(m * n));
+  PF_CHECK(group > 0 && k % group == 0, "%s: group_size=%lld must divide k=%lld", fname,
+           (long long)group, (long long)k);
+  PF_CHECK(numel(s) == n * (k / group), "%s: scales must be [N, K/group]", fname);
+  rb200_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.struct_size = sizeof(d);
+  if (parse_names(fname, act, bin, un, &d)) return -1;
+  d.weight_bits = 4;
+  d.x = data_of(x);
+  d.w = data_of(w);
+  d.scales = data_of(s);
+  if (z) {
+    if (check_tensor(fname, "zeros", z, kDLFloat, 16)) return -1;
+    PF_CHECK(numel(z) == numel(s), "%s: zeros must have the shape of scales", fname);
+    d.zeros = data_of(z);
+  }
+  if (bias) {
+    if (check_tensor(fname, "bias", bias, kDLFloat, 16)) return -1;
+    PF_CHECK(numel(bias) == n || numel(bias) == m * n, "%s: bias must be [n] or [m, n]", fname);
+    d.bias = data_of(bias);
+    d.bias_stride = (numel(bias) == n) ? 0 : n;
+  }
+  if (res) {
+    if (check_tensor(fname, "residual", res, kDLFloat, 16)) return -1;
+    PF_CHECK(numel(res) == m * n, "%s: residual must have m*n elements", fname);
+    d.residual = data_of(res);
+    if (d.binary_op == RB200_BIN_NONE) d.binary_op = RB200_BIN_PLUS;
+  }
+  d.out = data_of(out);
+  d.m = m;
+  d.n = n;
+  d.k = k;
+  d.ldx = k;
+  d.ldo = n;
+  d.group_size = group;
+  d.scale_stride_n = k / group;
+  d.scale_stride_g = 1;
+  d.zero_const = (float)zconst;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_gemm_fp16_intx(&d, rb200_get_stream());
+}
+
+// (w_pre, scales, zeros|null, layout, weight_bits, group_size, zero_const, out fp16 [N, K])
+int pf_dequantize(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
+  const char* fname = "relax_b200.dequantize";
+  Args a{v, tc, n_args, fname};
+  PF_CHECK(n_args == 8, "%s expects 8 arguments, got %d", fname, n_args);
+  const DLTensor *w, *s, *z, *out;
+  int64_t layout, bits, group;
+  double zconst;
+  if (a.tensor(0, &w) || a.tensor(1, &s) || a.tensor(2, &z, true) || a.integer(3, &layout) ||
+      a.integer(4, &bits) || a.integer(5, &group) || a.real(6, &zconst) || a.tensor(7, &out))
+    return -1;
+  if (check_tensor(fname, "scales", s, kDLFloat, 16) || check_tensor(fname, "out", out, kDLFloat, 16))
+    return -1;
+  PF_CHECK(out->ndim == 2, "%s: out must be [N, K]", fname);
+  const int64_t n = out->shape[0], k = out->shape[1];
+  PF_CHECK(numel(w) * (w->dtype.bits / 8) == n * k * bits / 8, "%s: weight bytes do not match [N, K]",
+           fname);
+  rb200_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.struct_size = sizeof(d);
+  d.weight_bits = (int)bits;
+  d.w = data_of(w);
+  d.scales = data_of(s);
+  d.zeros = z ? data_of(z) : nullptr;
+  d.n = n;
+  d.k = k;
+  const bool per_col = group <= 0 || group >= k;
+  d.group_size = per_col ? k : group;
+  if (layout == RB200_LAYOUT_FT_KN) {
+    d.scale_stride_n = 1;
+    d.scale_stride_g = per_col ? 0 : n;
+  } else {
+    d.scale_stride_n = per_col ? 1 : k / group;
+    d.scale_stride_g = per_col ? 0 : 1;
+  }
+  d.zero_const = (float)zconst;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_dequantize(&d, data_of(out), rb200_get_stream());
+}
+
+int pf_get_stream(RB200Value*, int*, int, RB200Value* ret, int* ret_tc, void*) {
+  if (ret) ret->v_handle = rb200_get_stream();
+  if (ret_tc) *ret_tc = RB200_ARG_HANDLE;
+  return 0;
+}
+int pf_set_stream(RB200Value* v, int* tc, int n, RB200Value*, int* ret_tc, void*) {
+  PF_CHECK(n == 1 && (tc[0] == (int)RB200_ARG_HANDLE || tc[0] == (int)RB200_ARG_NULL ||
+                      tc[0] == (int)RB200_ARG_INT),
+           "runtime.set_cuda_stream expects one handle");
+  rb200_set_stream(tc[0] == (int)RB200_ARG_NULL ? nullptr
+                   : tc[0] == (int)RB200_ARG_INT ? reinterpret_cast<void*>(v[0].v_int64)
+                                                 : v[0].v_handle);
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return 0;
+}
+
+void register_builtin(const char* name, RB200PackedCFunc fn) {
+  registry()[name] = new Entry{fn, nullptr, name};
+}
+
+void ensure_builtins() {
+  static bool done = false;
+  if (done) return;
+  done = true;
+  register_builtin("cutlass.ft_preprocess_weight", pf_ft_preprocess_weight);
+  register_builtin("relax_b200.preprocess_weight_q4f16", pf_preprocess_q4f16);
+  register_builtin("cutlass.ft_gemm_fp16_int4", pf_ft_gemm_int4);
+  register_builtin("cutlass.ft_gemm_fp16_int8", pf_ft_gemm_int8);
+  register_builtin("relax_b200.gemm_fp16_q4f16", pf_gemm_q4f16);
+  register_builtin("relax_b200.dequantize", pf_dequantize);
+  register_builtin("runtime.get_cuda_stream", pf_get_stream);
+  register_builtin("runtime.set_cuda_stream", pf_set_stream);
+}
+
+}  // namespace
+
+namespace rb200 {
+// other translation units add their operators here (grouped GEMM, collectives)
+void register_packed(const char* name, RB200PackedCFunc fn) {
+  std::lock_guard<std::mutex> lock(reg_mutex());
+  ensure_builtins();
+  registry()[name] = new Entry{fn, nullptr, name};
+}
+}  // namespace rb200
+
+extern "C" {
+
+int RB200FuncGetGlobal(const char* name, RB200FunctionHandle* out) {
+  std::lock_guard<std::mutex> lock(reg_mutex());
+  ensure_builtins();
+  PF_CHECK(name && out, "RB200FuncGetGlobal: NULL argument");
+  auto it = registry().find(name);
+  *out = it == registry().end() ? nullptr : it->second;  // NULL handle = not found, as TVMFuncGetGlobal
+  return 0;
+}
+
+int RB200FuncCall(RB200FunctionHandle func, RB200Value* arg_values, int* type_codes, int num_args,
+                  RB200Value* ret_val, int* ret_type_code) {
+  PF_CHECK(func != nullptr, "RB200FuncCall: NULL function handle");
+  Entry* e = static_cast<Entry*>(func);
+  RB200Value dummy;
+  int dummy_tc = RB200_ARG_NULL;
+  return e->fn(arg_values, type_codes, num_args, ret_val ? ret_val : &dummy,
+               ret_type_code ? ret_type_code : &dummy_tc, e->resource);
+}
+
+int RB200FuncRegisterGlobal(const char* name, RB200PackedCFunc f, void* resource_handle, int override) {
+  std::lock_guard<std::mutex> lock(reg_mutex());
+  ensure_builtins();
+  PF_CHECK(name && f, "RB200FuncRegisterGlobal: NULL argument");
+  auto it = registry().find(name);
+  PF_CHECK(it == registry().end() || override, "global function '%s' is already registered", name);
+  registry()[name] = new Entry{f, resource_handle, name};
+  return 0;
+}
+
+int RB200FuncListGlobalNames(int* out_size, const char*** out_array) {
+  std::lock_guard<std::mutex> lock(reg_mutex());
+  ensure_builtins();
+  static thread_local std::vector<const char*> names;
+  names.clear();
+  for (auto& kv : registry()) names.push_back(kv.second->name.c_str());
+  *out_size = (int)names.size();
+  *out_array = names.data();
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,99 @@
+// Weight repack into the fragment layout (see dequant.cuh), one 16-byte lane unit per thread.
+// Stands in for fastertransformer::preprocess_weights as called by
+// cutlass.ft_preprocess_weight (src/runtime/contrib/cutlass/weight_preprocess.cc:38-58): same
+// byte size in and out, signed codes biased to unsigned, layout private to the matmul kernels.
+#include "common.cuh"
+#include "preprocess.h"
+
+namespace rb200 {
+namespace {
+
+// Unsigned code of logical element (n, k) of one expert in the given source layout.
+template <int BITS, int LAYOUT>
+__device__ __forceinline__ uint32_t load_code(const uint8_t* src, int64_t n, int64_t k, int64_t K,
+                                              int64_t N) {
+  if (LAYOUT == 0) {  // FT: int8 container [K, N/2] (int4) or [K, N] (int8), signed
+    if (BITS == 4) {
+      uint32_t b = src[k * (N / 2) + (n >> 1)];
+      return ((b >> ((n & 1) * 4)) & 15u) ^ 8u;  // two's-complement nibble + 8
+    }
+    return (uint32_t)src[k * N + n] ^ 0x80u;  // signed byte + 128
+  }
+  // q4f16_1: uint32 [N, K/8], nibble j of a word = element 8*word + j, unsigned
+  uint32_t b = src[n * (K / 2) + (k >> 1)];
+  return (b >> ((k & 1) * 4)) & 15u;
+}
+
+template <int BITS, int LAYOUT>
+__global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                              int64_t K, int64_t N, int64_t units_per_expert, int64_t total_units) {
+  constexpr int kFrag = BITS == 4 ? 64 : 32;
+  const int64_t expert_bytes = K * N * BITS / 8;
+  for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total_units;
+       u += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e = u / units_per_expert;
+    const int64_t r = u % units_per_expert;
+    const int lane = (int)(r & 31);
+    const int64_t tile = r >> 5;
+    const int64_t KB = K / kFrag;
+    const int64_t nb = tile / KB, kb = tile % KB;
+    const int g = lane >> 2, t = lane & 3;
+    const uint8_t* s = src + e * expert_bytes;
+    uint32_t words[4];
+    if (BITS == 4) {
+      const int64_t k0 = kb * 64 + t * 16;
+      // nibble slot p of a word <- (row offset, k offset inside the word's 4 k)
+      const int row_of[8] = {0, 8, 0, 8, 0, 8, 0, 8};
+      const int k_of[8] = {0, 0, 2, 2, 1, 1, 3, 3};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          uint32_t c = load_code<BITS, LAYOUT>(s, nb * 16 + g + row_of[p], k0 + 4 * j + k_of[p], K, N);
+          w |= c << (4 * p);
+        }
+        words[j] = w;
+      }
+    } else {
+      const int64_t k0 = kb * 32 + t * 8;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int r8 = 0; r8 < 2; ++r8) {
+          uint32_t w = 0;
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4)
+            w |= load_code<BITS, LAYOUT>(s, nb * 16 + g + 8 * r8, k0 + 4 * j + c4, K, N) << (8 * c4);
+          words[2 * j + r8] = w;
+        }
+    }
+    reinterpret_cast<uint4*>(dst + e * expert_bytes)[r] = make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
+}  // namespace
+
+int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, int64_t n, int bits,
+                      int layout, cudaStream_t stream) {
+  const int64_t units = k * n * bits / 8 / 16;
+  const int64_t total = units * experts;
+  const int threads = 256;
+  int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks == 0) return 0;
+  const uint8_t* s = static_cast<const uint8_t*>(src);
+  uint8_t* d = static_cast<uint8_t*>(dst);
+  if (bits == 4 && layout == 0)
+    repack_kernel<4, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+  else if (bits == 4 && layout == 1)
+    repack_kernel<4, 1><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+  else if (bits == 8 && layout == 0)
+    repack_kernel<8, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+  else
+    RB200_CHECK(false, "unsupported preprocess combination bits=%d layout=%d", bits, layout);
+  RB200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace rb200

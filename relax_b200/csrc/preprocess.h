@@ -1,0 +1,6 @@
+#pragma once
+#include "common.cuh"
+namespace rb200 {
+int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, int64_t n, int bits,
+                      int layout, cudaStream_t stream);
+}

@@ -1,0 +1,66 @@
+"""Typed convenience wrappers over the global PackedFuncs (what a Python user of the reference
+would write with ``tvm.get_global_func`` + ``relax`` ops for this path)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .packed_func import get_global_func
+
+LAYOUT_FT_KN = 0
+LAYOUT_Q4_NK = 1
+
+
+def preprocess_weight_ft(packed_weight: torch.Tensor, is_int4: bool, sm: int = 100) -> torch.Tensor:
+    """``cutlass.ft_preprocess_weight(packed_weight, sm, is_int4)``
+    (src/runtime/contrib/cutlass/weight_preprocess.cc:38-58)."""
+    return get_global_func("cutlass.ft_preprocess_weight")(packed_weight, int(sm), bool(is_int4))
+
+
+def preprocess_weight_q4f16(packed_weight: torch.Tensor) -> torch.Tensor:
+    """Repack a q4f16_1 weight (uint32 [N, K/8], tests/python/dlight/test_gpu_gemv.py:189)."""
+    return get_global_func("relax_b200.preprocess_weight_q4f16")(packed_weight)
+
+
+def gemm_fp16_ft(x, w_pre, scales, weight_bits: int, bias=None, residual=None,
+                 activation: str = "identity", binary_op: str = "", unary_op: str = "identity",
+                 group_size: int = -1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(x @ decode(w) + bias)`` (optionally combined with a residual) for FT-layout weights:
+    the call python/tvm/contrib/cutlass/gemm_operation.py:441-458 emits."""
+    k = x.shape[-1]
+    n = w_pre.shape[-1] * (2 if weight_bits == 4 else 1)
+    m = x.numel() // k
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n, dtype=torch.float16, device=x.device)
+    bias_stride = 0
+    if bias is not None and bias.numel() == m * n and m > 1:
+        bias_stride = n
+    name = "cutlass.ft_gemm_fp16_int4" if weight_bits == 4 else "cutlass.ft_gemm_fp16_int8"
+    get_global_func(name)(x, w_pre, scales, bias, residual, activation, binary_op, unary_op, m, n, k,
+                          int(group_size if group_size > 0 else k), bias_stride, out)
+    return out
+
+
+def gemm_fp16_q4f16(x, w_pre, scales, zeros=None, bias=None, residual=None,
+                    activation: str = "identity", binary_op: str = "", unary_op: str = "identity",
+                    group_size: int = 32, zero_const: float = 7.0,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode + matmul for q4f16_1-layout weights (tests/python/dlight/test_gpu_gemv.py:193-206),
+    fp32 accumulation, fp16 output."""
+    n = w_pre.shape[0]
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n, dtype=torch.float16, device=x.device)
+    get_global_func("relax_b200.gemm_fp16_q4f16")(x, w_pre, scales, zeros, bias, residual, activation,
+                                                  binary_op, unary_op, int(group_size),
+                                                  float(zero_const), out)
+    return out
+
+
+def dequantize(w_pre, scales, n: int, k: int, weight_bits: int, layout: int, zeros=None,
+               group_size: int = -1, zero_const: float = 7.0) -> torch.Tensor:
+    """The dequantised weight fp16 [N, K] exactly as the matmul kernels form it."""
+    out = torch.empty(n, k, dtype=torch.float16, device=w_pre.device)
+    get_global_func("relax_b200.dequantize")(w_pre, scales, zeros, int(layout), int(weight_bits),
+                                             int(group_size), float(zero_const), out)
+    return out

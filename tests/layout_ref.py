@@ -1,0 +1,27 @@
+"""numpy statement of the fragment layout (test infrastructure): the expected bytes of
+rb200_preprocess_weight for a matrix of unsigned codes.  Written from the layout description in
+relax_b200/csrc/dequant.cuh, independently of the CUDA repack kernel."""
+import numpy as np
+
+
+def fragment_layout(codes: np.ndarray, bits: int) -> np.ndarray:
+    """codes uint8 [N, K] (unsigned) -> uint8 flat array of N*K*bits/8 bytes."""
+    n, k = codes.shape
+    if bits == 4:
+        kb = k // 64
+        # [nb, r2, g, kb, t, j, c] with n = nb*16 + r2*8 + g, k = kb*64 + t*16 + j*4 + c
+        c = codes.reshape(n // 16, 2, 8, kb, 4, 4, 4).astype(np.uint32)
+        # nibble slot p for (r2, c): c=0 -> p=0/1, c=1 -> p=4/5, c=2 -> p=2/3, c=3 -> p=6/7
+        slot = np.array([[0, 4, 2, 6], [1, 5, 3, 7]])
+        words = np.zeros((n // 16, 8, kb, 4, 4), dtype=np.uint32)  # [nb, g, kb, t, j]
+        for r2 in range(2):
+            for cc in range(4):
+                words |= c[:, r2, :, :, :, :, cc] << np.uint32(4 * slot[r2, cc])
+        # memory order: nb, kb, lane = g*4 + t, j
+        out = words.transpose(0, 2, 1, 3, 4).reshape(-1)
+        return out.astype("<u4").view(np.uint8)
+    kb = k // 32
+    # [nb, r2, g, kb, t, j, c] with k = kb*32 + t*8 + j*4 + c
+    c = codes.reshape(n // 16, 2, 8, kb, 4, 2, 4)
+    # memory order: nb, kb, g, t, j, r2, c
+    return np.ascontiguousarray(c.transpose(0, 3, 2, 4, 5, 1, 6)).reshape(-1).astype(np.uint8)
