@@ -1,0 +1,407 @@
+"""Benchmark of the decode hot path: W4A16 (group 32, q4f16_1 layout) GEMV over the Llama-2-7B
+decode linears (QKV 4096->12288, O 4096->4096, gate_up 4096->22016, down 11008->4096) at
+M in {1, 8, 32}.  One step = one pass over those 12 dequantize-matmul calls.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line.  `value` is aggregate algorithmic GB/s (each operand counted once:
+packed weight + scales + x + out) with every operand resident in HBM; `e2e` is the same metric
+through the PackedFunc surface with x and out in pinned HOST memory (copies inside the timed
+region, weights resident as model parameters, as the reference keeps them after
+`packed_weight.copyto(dev)`); `roofline` is the decode kernel's per-launch bandwidth against the
+measured HBM copy peak; `cpu_baseline` is the CPU oracle (a port of the reference's CPU lowering:
+materialise the decoded weight, then an fp32 matmul) on a bounded sample.
+
+N > 1 (one process per GPU under torchrun): weak scaling of Megatron-style shards - every rank
+holds full-size shards of a g-times wider layer; column-parallel layers (QKV, gate_up) need no
+communication, row-parallel layers (O, down) end in an NCCL all-reduce of the [M, 4096] output.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "W4A16 GEMV HBM GB/s"
+UNIT = "GB/s"
+MS = (1, 8, 32)
+GROUP = 32
+WEIGHT_SETS = 4  # rotated so that a weight is evicted from the 126 MB L2 before it is reused
+
+
+def linears():
+    from relax_b200 import synth
+    return synth.LLAMA7B_LINEARS
+
+
+def step_bytes():
+    from relax_b200 import synth
+    return sum(synth.algorithmic_bytes(m, n, k, 4, GROUP) for m in MS for _, k, n in linears())
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- CPU arms
+def cpu_sample(target_seconds: float):
+    """Times the CPU port on a bounded sample of the step: the first `rows` output rows of each
+    linear at every M, sized from a probe so that one sample takes about `target_seconds`."""
+    from oracle import oracle as orc
+    from relax_b200 import synth
+    C = orc.C()
+    g = np.random.Generator(np.random.PCG64(1000))
+    cases = {}
+    for name, k, n in linears():
+        rows = min(n, 2048)
+        cases[name] = synth.q4_case(g, max(MS), k, rows, GROUP)
+    # probe: 256 rows of every linear at every M
+    t0 = time.perf_counter()
+    for name, k, n in linears():
+        c = cases[name]
+        for m in MS:
+            C.baseline_q4_nk(c.x[:m], c.w, c.scales, GROUP, 0, 256)
+    probe = time.perf_counter() - t0
+    rows = int(max(16, min(2048, 256 * target_seconds / max(probe, 1e-6)))) // 16 * 16
+
+    def run_once():
+        t = time.perf_counter()
+        for name, k, n in linears():
+            c = cases[name]
+            for m in MS:
+                C.baseline_q4_nk(c.x[:m], c.w, c.scales, GROUP, 0, rows)
+        return time.perf_counter() - t
+
+    nbytes = sum(synth.algorithmic_bytes(m, rows, k, 4, GROUP) for m in MS for _, k, _n in linears())
+    sample = "first %d output rows of each of the 4 linears, M in {1,8,32}" % rows
+    return run_once, nbytes, C.num_threads, sample
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU lowering of the path (decode materialised, then an fp32
+    matmul), timed on the host cores.  The reference's own TVM/LLVM build cannot be produced on
+    this machine, so this is the C port of that lowering (oracle/), with all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    run_once, nbytes, threads, sample = cpu_sample(1.5)
+    for _ in range(args.warmup):
+        run_once()
+    t = 0.0
+    for _ in range(args.steps):
+        t += run_once()
+    value = nbytes * args.steps / t / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "Llama-2-7B decode linears W4A16 group-32 symmetric (q4f16_1), M in {1,8,32}: "
+                    "QKV K=4096 N=12288; O K=4096 N=4096; gate_up K=4096 N=22016; down K=11008 N=4096",
+        "launches_per_step": len(MS) * 4,
+        "l2": "inputs larger than L2: %d distinct weight sets (%.0f MB) rotated, each evicted before reuse"
+              % (WEIGHT_SETS, WEIGHT_SETS * 113.97),
+        "parallelism": "single GPU" if n_gpus == 1 else
+        "tp%d weak: full-size Megatron shards per rank, all-reduce after row-parallel O and down" % n_gpus,
+    }
+
+
+# --------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for ln in open(self.path):
+                f = [x.strip() for x in ln.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import relax_b200
+    from relax_b200 import ops, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1000 + rank)
+    lin = linears()
+    row_parallel = {"o", "down"}
+
+    # resident parameters: WEIGHT_SETS x 4 linears, repacked once by the preprocess entry point
+    sets = []
+    for s_i in range(WEIGHT_SETS):
+        layer = {}
+        for name, k, n in lin:
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), dtype=torch.int32, device=dev, generator=gen)
+            sc = (torch.rand((n, k // GROUP), device=dev, generator=gen) * 0.009 + 0.001).to(torch.float16)
+            layer[name] = (ops.preprocess_weight_q4f16(w), sc, w if s_i == 0 else None)
+            del w
+        sets.append(layer)
+    xs = {(name, m): torch.randn((m, k), device=dev, generator=gen).to(torch.float16)
+          for name, k, n in lin for m in MS}
+    outs = {(name, m): torch.empty((m, n), dtype=torch.float16, device=dev) for name, k, n in lin for m in MS}
+    torch.cuda.synchronize()
+
+    # ---- parity spot check against the CPU oracle (rank 0, one linear, a row sample)
+    max_rel_err = None
+    if rank == 0:
+        from oracle import oracle as orc
+        name, k, n = lin[1]
+        pre, sc, w_raw = sets[0][name]
+        got = ops.gemm_fp16_q4f16(xs[(name, 8)], pre, sc).float().cpu().numpy()
+        C = orc.C()
+        wq = C.decode_q4_nk(w_raw.cpu().numpy().view(np.uint32)[:512], sc.cpu().numpy()[:512], None, 7.0, GROUP)
+        exp = C.epilogue(C.matmul_f32(xs[(name, 8)].cpu().numpy(), wq)).astype(np.float32)
+        max_rel_err = float(np.max(np.abs(got[:, :512] - exp)) / np.max(np.abs(exp)))
+        assert max_rel_err <= 1e-2, "bench parity check failed: %g" % max_rel_err
+    for layer in sets:
+        for name in layer:
+            layer[name] = layer[name][:2]
+
+    counter = {"launches": 0}
+
+    def one_step(step_idx, events=None):
+        for mi, m in enumerate(MS):
+            layer = sets[(step_idx * len(MS) + mi) % WEIGHT_SETS]
+            for name, k, n in lin:
+                pre, sc = layer[name]
+                if events is not None:
+                    e0 = torch.cuda.Event(enable_timing=True)
+                    e1 = torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                ops.gemm_fp16_q4f16(xs[(name, m)], pre, sc, out=outs[(name, m)])
+                counter["launches"] += 1
+                if events is not None:
+                    e1.record()
+                    events.append((e0, e1, synth.algorithmic_bytes(m, n, k, 4, GROUP)))
+                if world > 1 and name in row_parallel:
+                    dist.all_reduce(outs[(name, m)])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: the step is launch-bound from Python (kernels of 3-12 us), so
+    # each of the WEIGHT_SETS rotation phases is captured once in a CUDA graph and replayed
+    for i in range(max(args.warmup, WEIGHT_SETS)):
+        one_step(i)
+    barrier()
+    graphs = []
+    use_graphs = os.environ.get("RB200_BENCH_NO_GRAPH", "0") != "1"
+    if use_graphs:
+        try:
+            for ph in range(WEIGHT_SETS):
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_):
+                    one_step(ph)
+                graphs.append(g_)
+        except Exception as exc:  # capture of the collective refused: time eager launches instead
+            if rank == 0:
+                sys.stderr.write("graph capture unavailable (%s); timing eager launches\n" % exc)
+            graphs = []
+            torch.cuda.synchronize()
+
+    def timed_step(i):
+        if graphs:
+            graphs[i % WEIGHT_SETS].replay()
+            counter["launches"] += len(MS) * len(lin)
+        else:
+            one_step(i)
+
+    for i in range(args.warmup):
+        timed_step(i)
+    barrier()
+    clocks = ClockSampler(local)
+    clocks.start()
+    counter["launches"] = 0
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for i in range(args.steps):
+        timed_step(args.warmup + i)
+    t1.record()
+    barrier()
+    ms_total = t0.elapsed_time(t1)
+    launches = counter["launches"]
+
+    # ---- per-launch roofline pass: eager launches with events around every launch, queued behind
+    # a spin kernel so the host runs ahead and the events bracket device time only
+    events = []
+    for i in range(args.steps):
+        torch.cuda._sleep(3_000_000)
+        one_step(args.warmup + args.steps + i, events)
+        if i % 8 == 7:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    dur = [a.elapsed_time(b) for a, b, _ in events]
+    byt = [c for _, _, c in events]
+    achieved = (sum(byt) / len(byt)) / (sum(dur) / len(dur) * 1e-3) / 1e9
+    per_shape = {}
+    labels = [(m, name) for _ in range(args.steps) for m in MS for name, _, _ in lin]
+    for (a, b, c), (m_, name_) in zip(events, labels):
+        per_shape.setdefault("%s_m%d" % (name_, m_), []).append((a.elapsed_time(b), c))
+    shape_gbs = {k_: round(sum(c for _, c in v) / (sum(t for t, _ in v) * 1e-3) / 1e9, 1) for k_, v in per_shape.items()}
+
+    # ---- end-to-end timing through the PackedFunc surface with host buffers
+    hx = {key: t.cpu().pin_memory() for key, t in xs.items()}
+    hout = {key: torch.empty_like(t, device="cpu").pin_memory() for key, t in outs.items()}
+    h2d = sum(t.numel() * 2 for t in hx.values())
+    d2h = sum(t.numel() * 2 for t in hout.values())
+
+    def e2e_step(step_idx):
+        for mi, m in enumerate(MS):
+            layer = sets[(step_idx * len(MS) + mi) % WEIGHT_SETS]
+            for name, k, n in lin:
+                pre, sc = layer[name]
+                xs[(name, m)].copy_(hx[(name, m)], non_blocking=True)
+                ops.gemm_fp16_q4f16(xs[(name, m)], pre, sc, out=outs[(name, m)])
+                if world > 1 and name in row_parallel:
+                    dist.all_reduce(outs[(name, m)])
+                hout[(name, m)].copy_(outs[(name, m)], non_blocking=True)
+        torch.cuda.synchronize()  # the step's results are on the host
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(args.warmup + i)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clk = clocks.stop()
+
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = float(t[0]), float(t[1])
+
+    sb = step_bytes()
+    value = world * sb * args.steps / (ms_total * 1e-3) / 1e9
+    e2e_value = world * sb * args.steps / (ms_e2e * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+
+    cpu = None
+    if rank == 0 and world == 1:
+        run_once, nbytes, threads, sample = cpu_sample(12.0)
+        t = run_once()
+        cpu = {"value": nbytes / t / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": sample + " (%.1f s of CPU work)" % t}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": dict(workload_config(world), timed_with="cuda graph replay" if graphs else "eager launches"),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "gemv_kernel", "per_shape_gbs": shape_gbs},
+            "cpu_baseline": cpu,
+            "clocks": {"sm_mhz": clk["sm_mhz"], "sm_max_mhz": clk["sm_max_mhz"], "reasons": clk["reasons"]},
+            "max_rel_err_vs_oracle": max_rel_err,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

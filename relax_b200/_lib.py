@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "librelax_b200.so")
+# RELAX_B200_LIBRARY overrides the in-tree location (e.g. an instrumented build of the same sources)
+LIB_PATH = os.environ.get("RELAX_B200_LIBRARY") or os.path.join(_PKG, "librelax_b200.so")
 
 
 class GemmDesc(ctypes.Structure):

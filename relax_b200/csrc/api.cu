@@ -243,9 +243,9 @@ size_t rb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int weight_bi
 int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
   if (validate_common(d) != 0) return -1;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  RB200_CHECK(d->x && d->out, "x and out must be non-NULL");
   RB200_CHECK(d->m >= 0, "m must be >= 0");
-  if (d->m == 0) return 0;
+  if (d->m == 0) return 0;  // empty batch: nothing to launch (pointers of empty tensors may be NULL)
+  RB200_CHECK(d->x && d->out, "x and out must be non-NULL");
   const int64_t ldx = d->ldx > 0 ? d->ldx : d->k;
   const int64_t ldo = d->ldo > 0 ? d->ldo : d->n;
   RB200_CHECK(aligned16(d->x) && ldx % 8 == 0, "x must be 16-byte aligned with ldx %% 8 == 0");
@@ -304,6 +304,12 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
+#ifdef RB200_ABLATE
+    {
+      const char* ab = getenv("RB200_GEMV_ABLATE");
+      p.ablate = ab ? atoi(ab) : 0;
+    }
+#endif
     return gemv_launch(p, plan, d->weight_bits, zero_mode(d), stream);
   }
   return gemm_tc_launch(d, epi, group, zero_mode(d), stream);

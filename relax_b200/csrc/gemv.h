@@ -25,6 +25,9 @@ struct GemvParams {
   int stages;
   int chunks_per_tile;
   long long total_iters;
+#ifdef RB200_ABLATE
+  int ablate;
+#endif
 };
 
 struct GemvPlan {

@@ -125,12 +125,16 @@ def _wrap_preprocess(pf: PackedFunc) -> Callable:
 
 
 _ALLOCATING = {"cutlass.ft_preprocess_weight", "relax_b200.preprocess_weight_q4f16"}
+_CACHE = {}
 
 
 def get_global_func(name: str, allow_missing: bool = False):
     """``tvm.get_global_func`` counterpart.  Destination-passing operators are returned as is;
     the preprocess functions are wrapped so that they allocate and return their result, like the
     reference's."""
+    hit = _CACHE.get(name)
+    if hit is not None:
+        return hit
     lib = _lib.load()
     h = ctypes.c_void_p()
     _lib.check(lib.RB200FuncGetGlobal(name.encode(), ctypes.byref(h)))
@@ -139,4 +143,6 @@ def get_global_func(name: str, allow_missing: bool = False):
             return None
         raise ValueError("Cannot find global function %s" % name)
     pf = PackedFunc(name, h.value)
-    return _wrap_preprocess(pf) if name in _ALLOCATING else pf
+    fn = _wrap_preprocess(pf) if name in _ALLOCATING else pf
+    _CACHE[name] = fn
+    return fn
