@@ -91,7 +91,7 @@ def load() -> ctypes.CDLL:
         return _lib
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
-            "relax_b200: %s is missing - build it with `python -m relax_b200.build`; there is no "
+            "relax_b200: %s is missing - build it with `python relax_b200/build.py`; there is no "
             "fallback path" % LIB_PATH)
     lib = ctypes.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():

@@ -1,6 +1,6 @@
 """Builds ``librelax_b200.so`` in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-Usage: ``python -m relax_b200.build [--force]``.  Objects go to ``relax_b200/build/``; a source
+Usage: ``python relax_b200/build.py [--force]``.  Objects go to ``relax_b200/build/``; a source
 is recompiled only when it, or any header next to it, is newer than its object.
 """
 from __future__ import annotations
