@@ -133,6 +133,25 @@ RB200_API int rb200_gemm_fp16_int_bias_act_residual(
     int k, int group_size, int weight_bits, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * No counterpart in the reference: the same decode-path computation as rb200_gemm_fp16_intx for
+ * hosts that must not allocate device memory while running - runtimes whose own pool already
+ * owns the whole device (a driver allocation from inside the library would fail), and serving
+ * loops that forbid driver allocation calls on their hot thread because such calls stall the
+ * device.  This entry point calls no cudaMalloc / cudaFree and no allocating library routine:
+ * its split-k scratch is a fixed array inside the library image (about 5.06 MiB of device
+ * memory on every GPU that loads the library, held until the process exits).
+ *   Limits : m <= 16 and n <= 262144 (anything larger is rejected with an error, as is a
+ *            problem whose partials would not fit); `workspace` in the descriptor is ignored.
+ *   Set-up : the first call on each device resolves the array's device address and queries the
+ *            device; make that first call with the device current and before any stream capture.
+ *   Sharing: every call on a device uses the same array.  Each call clears the tickets and the
+ *            status word it needs on `stream` before launching, so calls issued in stream order
+ *            are independent; calls that overlap on the GPU (different streams, no dependency
+ *            between them) race on the array and give undefined results.
+ */
+RB200_API int rb200_gemm_fp16_intx_noalloc(const rb200_gemm_desc* desc, void* stream);
+
+/*
  * Debug/verification entry: writes the dequantised weight wq fp16 [n, k] (row-major) that the
  * matmul kernels feed to the tensor cores, produced by the same device decode routine.  Uses
  * the w / scales / zeros / group / stride / zero_const fields of the descriptor.  The arithmetic
