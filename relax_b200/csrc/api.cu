@@ -7,6 +7,7 @@
 #include "../../include/relax_b200.h"
 #include "dequant.cuh"
 #include "gemv.h"
+#include "gemv_cluster.cuh"
 #include "gemm_tc.h"
 #include "preprocess.h"
 
@@ -262,7 +263,33 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
   epi.unop = d->unary_op;
   const int group = (d->group_size <= 0 || d->group_size >= d->k) ? 0 : (int)d->group_size;
 
+  static const bool force_scratch_path = getenv("RB200_GEMV_SCRATCH_PATH") != nullptr;
+  if (d->m <= 32 && !d->workspace && !force_scratch_path) {
+    // default decode path: cluster split-k, no global scratch beyond the status word
+    DeviceScratch* sc = device_scratch(0, 0);
+    if (!sc) return -1;
+    GemvParams p;
+    memset(&p, 0, sizeof(p));
+    p.status = sc->status;
+    p.x = static_cast<const __half*>(d->x);
+    p.ldx = ldx;
+    p.w = static_cast<const uint8_t*>(d->w);
+    p.s = static_cast<const __half*>(d->scales);
+    p.z = static_cast<const __half*>(d->zeros);
+    p.s_n = d->scale_stride_n;
+    p.s_g = d->scale_stride_g;
+    p.out = static_cast<__half*>(d->out);
+    p.ldo = ldo;
+    p.epi = epi;
+    p.m = (int)d->m;
+    p.n = (int)d->n;
+    p.k = (int)d->k;
+    p.group = group;
+    p.zero_const = d->zero_const;
+    return gemv_cluster_run(p, d->weight_bits, zero_mode(d), sc->sm_count, stream);
+  }
   if (d->m <= 32) {
+    // caller-provided workspace (or RB200_GEMV_SCRATCH_PATH): stream-k kernel with global partials
     DeviceScratch* sc = device_scratch(0, 0);
     if (!sc) return -1;
     GemvPlan plan;

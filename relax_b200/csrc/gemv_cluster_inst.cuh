@@ -1,0 +1,73 @@
+// Instantiation + dispatch of gemv_cluster_kernel for one weight width (included by the
+// per-width translation units so they compile in parallel).
+#pragma once
+#include "gemv_cluster.cuh"
+
+namespace rb200 {
+namespace gc {
+
+template <int BITS, int MT, int ZMODE, int GROUP, int SRC>
+int launch_inst(const ClusterParams& cp, const ClusterLaunch& l, const CUtensorMap& ts,
+                const CUtensorMap& tz, cudaStream_t stream) {
+  auto kern = gemv_cluster_kernel<BITS, MT, ZMODE, GROUP, SRC>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  RB200_CUDA(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    RB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_device = dev;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)l.grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = l.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)l.split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  RB200_CUDA(cudaLaunchKernelEx(&cfg, kern, cp, ts, tz));
+  return 0;
+}
+
+template <int BITS, int MT, int ZMODE>
+int launch_gs(const ClusterParams& cp, const ClusterLaunch& l, const CUtensorMap& ts,
+              const CUtensorMap& tz, cudaStream_t stream) {
+#define RB200_CASE(G, S) \
+  if (l.group_code == (G) && l.src == (S)) return launch_inst<BITS, MT, ZMODE, G, S>(cp, l, ts, tz, stream)
+  RB200_CASE(32, kSrcGlobal);
+  RB200_CASE(64, kSrcGlobal);
+  RB200_CASE(128, kSrcGlobal);
+  RB200_CASE(0, kSrcGlobal);
+  RB200_CASE(-1, kSrcGlobal);
+  if (BITS == 4) RB200_CASE(32, kSrcSmemNK);
+  RB200_CASE(32, kSrcSmemKN);
+  RB200_CASE(64, kSrcSmemKN);
+  RB200_CASE(128, kSrcSmemKN);
+#undef RB200_CASE
+  RB200_CHECK(false, "no decode kernel for group code %d with scale source %d", l.group_code, l.src);
+  return -1;
+}
+
+template <int BITS>
+int launch_bits(const ClusterParams& cp, const ClusterLaunch& l, const CUtensorMap& ts,
+                const CUtensorMap& tz, cudaStream_t stream) {
+#define RB200_MZ(M, Z) \
+  if (l.mt == (M) && l.zmode == (Z)) return launch_gs<BITS, M, Z>(cp, l, ts, tz, stream)
+  RB200_MZ(1, kZeroConstInt);
+  RB200_MZ(2, kZeroConstInt);
+  RB200_MZ(4, kZeroConstInt);
+  RB200_MZ(1, kZeroGeneral);
+  RB200_MZ(2, kZeroGeneral);
+  RB200_MZ(4, kZeroGeneral);
+#undef RB200_MZ
+  RB200_CHECK(false, "bad m-tile count %d / zero mode %d", l.mt, l.zmode);
+  return -1;
+}
+
+}  // namespace gc
+}  // namespace rb200
