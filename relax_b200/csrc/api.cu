@@ -8,6 +8,7 @@
 #include "dequant.cuh"
 #include "gemv.h"
 #include "gemv_cluster.cuh"
+#include "umma_gemv.cuh"
 #include "gemm_tc.h"
 #include "preprocess.h"
 
@@ -286,6 +287,15 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
+    {
+      // tensor-core (tcgen05) decode kernel where it applies; epoch flags live past the ticket area
+      constexpr size_t kFlagOffset = 49152, kFlagCount = 16384;
+      const unsigned epoch = ++sc->epoch;
+      const int rc = umma_gemv_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials,
+                                   sc->partial_bytes, reinterpret_cast<unsigned*>(sc->counters) + kFlagOffset,
+                                   kFlagCount, epoch, stream);
+      if (rc <= 0) return rc;
+    }
     return gemv_cluster_run(p, d->weight_bits, zero_mode(d), sc->sm_count, stream);
   }
   if (d->m <= 32) {

@@ -43,6 +43,7 @@ struct DeviceScratch {
   float* partials = nullptr;
   size_t partial_bytes = 0;
   int sm_count = 0;
+  unsigned epoch = 0;       // launch counter for epoch-valued flags (tcgen05 decode kernel)
 };
 // Returns the current device's scratch, allocating it on first use (never inside a capture:
 // call once during warm-up).  nullptr + last error set on failure.

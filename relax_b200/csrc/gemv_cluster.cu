@@ -19,16 +19,6 @@ size_t cluster_stage_bytes(int bits, int mt, int zmode, int src) {
   return b;
 }
 
-// Cost of a split factor in units of "one k-chunk on a CTA that shares its SM with another":
-// waves of clusters over the resident slots times the chunks each CTA streams, plus a fixed
-// charge for the two cluster barriers and the DSMEM sum.
-static double split_cost(int n_tiles, int cpt, int s, int slots) {
-  const long long ctas = (long long)n_tiles * s;
-  const long long waves = (ctas + slots - 1) / slots;
-  const int per_cta = (cpt + s - 1) / s;
-  return (double)waves * per_cta + (s > 1 ? 1.5 : 0.0) + 0.35 * (waves - 1);
-}
-
 }  // namespace gc
 
 int gemv_cluster_run(const GemvParams& p_in, int bits, int zmode, int sm_count, cudaStream_t stream) {
@@ -105,34 +95,14 @@ int gemv_cluster_run(const GemvParams& p_in, int bits, int zmode, int sm_count, 
   static const int env_split = getenv("RB200_GEMV_SPLIT") ? atoi(getenv("RB200_GEMV_SPLIT")) : 0;
   static const int env_stages = getenv("RB200_GEMV_STAGES") ? atoi(getenv("RB200_GEMV_STAGES")) : 0;
   static const int env_ctas = getenv("RB200_GEMV_CTAS_PER_SM") ? atoi(getenv("RB200_GEMV_CTAS_PER_SM")) : 0;
-  const int ctas_per_sm = env_ctas > 0 ? env_ctas : 2;
-  const int slots = sm_count * ctas_per_sm;
-  int best = 1;
-  double best_cost = 1e30;
-  const int max_split = cpt < 8 ? cpt : 8;
-  for (int s = 1; s <= max_split; ++s) {
-    const double c = split_cost(n_tiles, cpt, s, slots);
-    if (c < best_cost - 1e-9) {
-      best_cost = c;
-      best = s;
-    }
-  }
-  if (env_split > 0) best = env_split < max_split ? env_split : max_split;
-  l.split = best;
-  cp.split = best;
-  l.grid = n_tiles * best;
-
-  const size_t sb = cluster_stage_bytes(bits, l.mt, zmode, l.src);
-  const size_t fixed = (size_t)kConsumerWarps * l.mt * 512 + 2 * 16 * sizeof(uint64_t);
-  const size_t budget = (size_t)(228 * 1024) / ctas_per_sm - 1024;
-  int stages = (int)((budget - fixed) / sb);
-  const int per_cta = (cpt + best - 1) / best;
-  if (stages > per_cta) stages = per_cta;  // never more stages than chunks a CTA will see
-  if (env_stages > 0) stages = env_stages;
-  if (stages > 16) stages = 16;
-  if (stages < 1) stages = 1;
-  p.stages = stages;
-  l.smem_bytes = (size_t)stages * sb + (size_t)kConsumerWarps * l.mt * 512 + (size_t)stages * 2 * sizeof(uint64_t);
+  l.n_tiles = n_tiles;
+  l.cpt = cpt;
+  l.sm_count = sm_count;
+  l.ctas_per_sm = env_ctas > 0 ? env_ctas : 2;
+  l.force_split = env_split;
+  l.force_stages = env_stages;
+  l.stage_bytes = cluster_stage_bytes(bits, l.mt, zmode, l.src);
+  l.fixed_bytes = (size_t)2 * kConsumerWarps * l.mt * 512;
 
   if (bits == 4) return launch_cluster_i4(cp, l, ts, tz, stream);
   return launch_cluster_i8(cp, l, ts, tz, stream);

@@ -4,10 +4,13 @@
 // with bulk async copies, eight consumer warps decode 128-bit fragment words in registers and
 // issue m16n8k16 MMAs with fp32 accumulators - with three differences that the profile of the
 // first version asked for:
-//   * split-k runs inside a thread-block cluster: the S CTAs of a cluster share one 128-row
-//     tile, each streams 1/S of its k-chunks, and the partial fragments are summed by the
-//     cluster's first CTA through distributed shared memory (two cluster barriers) instead of
-//     through global memory, fences and tickets;
+//   * split-k runs inside persistent thread-block clusters: the S CTAs of a cluster walk the
+//     128-row tiles together, each streaming 1/S of a tile's k-chunks; partial fragments are
+//     published in the CTA's own shared memory and summed through distributed shared memory by
+//     a leader that rotates from tile to tile.  Hand-off is two mbarriers per CTA ("partials of
+//     all ranks are ready" at the leader, "your partials were consumed" at each rank) with
+//     cluster-scope release/acquire, so the bulk-copy pipeline never drains between tiles and no
+//     global memory, fence or ticket is involved;
 //   * scales and zero points ride the same asynchronous pipeline (one TMA tile per stage) when
 //     their layout allows it, so no consumer waits on a global load;
 //   * each m-tile accumulates into two independent fragment chains, halving the MMA dependency
@@ -87,6 +90,34 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t ran
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
+// arrive on an mbarrier that lives in another CTA of the cluster (address from map_to_rank)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint64_t* bar, uint32_t parity, int* status) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (clock64() - t0 > (1ll << 31)) {
+      if (status) atomicExch(status, kStatusWaitTimeout);
+      return false;
+    }
+  }
+}
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -114,17 +145,21 @@ __global__ void __launch_bounds__(kThreads, 2)
   const GemvParams& p = cp.g;
 
   const int stages = p.stages;
-  // [stages][kStage] | reduction area 8 warps x MT x 2 chains?? (summed before) -> MT*4*32 floats per warp | barriers
-  float* red = reinterpret_cast<float*>(smem + (size_t)stages * kStage);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStage + kConsumerWarps * MT * 512);
-  uint64_t* empty_bar = full_bar + stages;
-
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int S = cp.split;
+  // [stages][kStage] | partial fragments red[2][8 warps][MT][4][32] fp32 | mbarriers
+  constexpr int kRedFloats = kConsumerWarps * MT * 128;  // one buffer
+  float* red = reinterpret_cast<float*>(smem + (size_t)stages * kStage);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStage + 2 * kRedFloats * 4);
+  uint64_t* empty_bar = full_bar + stages;
+  uint64_t* ready_bar = empty_bar + stages;  // [1]  leader side: every rank's warps published
+  uint64_t* free_bar = ready_bar + 1;        // [2]  per buffer: the leader has summed my partials
+
   const int rank = S > 1 ? (int)cluster_ctarank() : 0;
-  const int tile = blockIdx.x / S;
+  const int cluster_id = blockIdx.x / S;
+  const int n_clusters = gridDim.x / S;
 
   for (int s = 0; s < stages; ++s) {
     uint32_t* xs = reinterpret_cast<uint32_t*>(smem + (size_t)s * kStage + G::kWBytes);
@@ -135,73 +170,96 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
+    mbar_init(ready_bar, S * kConsumerWarps);
+    mbar_init(&free_bar[0], kConsumerWarps);
+    mbar_init(&free_bar[1], kConsumerWarps);
     mbar_fence_init();
   }
   fence_proxy_async();
   __syncthreads();
+  if (S > 1) cluster_sync_all();  // peers' mbarriers exist before anyone arrives on them
 
   const int cpt = p.chunks_per_tile;
   const int c0 = (int)((long long)rank * cpt / S);
   const int c1 = (int)((long long)(rank + 1) * cpt / S);
   const int kb_total = p.k / G::kFrag;
   const int n_blocks = p.n / 16;
-  const int blk0 = tile * kConsumerWarps;
-  const int nblk = min(kConsumerWarps, n_blocks - blk0);
+  const int n_tiles = (n_blocks + kConsumerWarps - 1) / kConsumerWarps;
 
   if (warp == kConsumerWarps) {
     // ------------------------------------------------------------ producer warp
     int stage = 0;
     uint32_t phase = 0;
-    for (int chunk = c0; chunk < c1; ++chunk) {
-      if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, p.status)) break;
-      const int kb0 = chunk * kBlocksPerChunk;
-      const int nkb = min(kBlocksPerChunk, kb_total - kb0);
-      uint8_t* sbase = smem + (size_t)stage * kStage;
-      const uint32_t wbytes = (uint32_t)nkb * kTileBytes;
-      const uint32_t xbytes = (uint32_t)nkb * G::kFrag * 2;
-      uint32_t tx = wbytes * nblk + xbytes * p.m;
-      if (SRC != kSrcGlobal) tx += cp.s_box_bytes * (cp.has_z_tile ? 2u : 1u);
-      if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], tx);
-      __syncwarp();
-      if (lane < nblk) {
-        const uint8_t* src = p.w + ((size_t)(blk0 + lane) * kb_total + kb0) * kTileBytes;
-        bulk_g2s(sbase + lane * (kBlocksPerChunk * kTileBytes), src, wbytes, &full_bar[stage]);
-      }
-      if (SRC != kSrcGlobal) {
-        // coordinates: NK tensor {group, row}; KN tensor {row, group}
-        constexpr int kGroupsPerChunk = GROUP > 0 ? (G::kChunk / GROUP) : 1;
-        const int gc0 = chunk * kGroupsPerChunk;
-        if (lane == 8) {
-          if (SRC == kSrcSmemNK) tma_load_2d(sbase + L::kSOff, &tmap_s, gc0, blk0 * 16, &full_bar[stage]);
-          else tma_load_2d(sbase + L::kSOff, &tmap_s, blk0 * 16, gc0, &full_bar[stage]);
+    bool ok = true;
+    for (int tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
+      const int blk0 = tile * kConsumerWarps;
+      const int nblk = min(kConsumerWarps, n_blocks - blk0);
+      for (int chunk = c0; chunk < c1; ++chunk) {
+        if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, p.status)) {
+          ok = false;
+          break;
         }
-        if (ZMODE == kZeroGeneral && lane == 9 && cp.has_z_tile) {
-          if (SRC == kSrcSmemNK) tma_load_2d(sbase + L::kZOff, &tmap_z, gc0, blk0 * 16, &full_bar[stage]);
-          else tma_load_2d(sbase + L::kZOff, &tmap_z, blk0 * 16, gc0, &full_bar[stage]);
+        const int kb0 = chunk * kBlocksPerChunk;
+        const int nkb = min(kBlocksPerChunk, kb_total - kb0);
+        uint8_t* sbase = smem + (size_t)stage * kStage;
+        const uint32_t wbytes = (uint32_t)nkb * kTileBytes;
+        const uint32_t xbytes = (uint32_t)nkb * G::kFrag * 2;
+        uint32_t tx = wbytes * nblk + xbytes * p.m;
+        if (SRC != kSrcGlobal) tx += cp.s_box_bytes * (cp.has_z_tile ? 2u : 1u);
+        if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], tx);
+        __syncwarp();
+        if (lane < nblk) {
+          const uint8_t* src = p.w + ((size_t)(blk0 + lane) * kb_total + kb0) * kTileBytes;
+          bulk_g2s(sbase + lane * (kBlocksPerChunk * kTileBytes), src, wbytes, &full_bar[stage]);
         }
-      }
-      for (int r = lane; r < p.m; r += 32) {
-        const __half* src = p.x + (size_t)r * p.ldx + (size_t)kb0 * G::kFrag;
-        bulk_g2s(sbase + G::kWBytes + r * G::kXPitch, src, xbytes, &full_bar[stage]);
-      }
-      if (++stage == stages) {
-        stage = 0;
-        phase ^= 1u;
+        if (SRC != kSrcGlobal) {
+          // coordinates: NK tensor {group, row}; KN tensor {row, group}
+          constexpr int kGroupsPerChunk = GROUP > 0 ? (G::kChunk / GROUP) : 1;
+          const int gc0 = chunk * kGroupsPerChunk;
+          if (lane == 8) {
+            if (SRC == kSrcSmemNK) tma_load_2d(sbase + L::kSOff, &tmap_s, gc0, blk0 * 16, &full_bar[stage]);
+            else tma_load_2d(sbase + L::kSOff, &tmap_s, blk0 * 16, gc0, &full_bar[stage]);
+          }
+          if (ZMODE == kZeroGeneral && lane == 9 && cp.has_z_tile) {
+            if (SRC == kSrcSmemNK) tma_load_2d(sbase + L::kZOff, &tmap_z, gc0, blk0 * 16, &full_bar[stage]);
+            else tma_load_2d(sbase + L::kZOff, &tmap_z, blk0 * 16, gc0, &full_bar[stage]);
+          }
+        }
+        for (int r = lane; r < p.m; r += 32) {
+          const __half* src = p.x + (size_t)r * p.ldx + (size_t)kb0 * G::kFrag;
+          bulk_g2s(sbase + G::kWBytes + r * G::kXPitch, src, xbytes, &full_bar[stage]);
+        }
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
-  } else {
-    // ------------------------------------------------------------ consumer warps
-    const int g = lane >> 2;
-    const int t = lane & 3;
-    const ZeroConsts zc = make_zero_consts(ZMODE, p.zero_const);
-    const uint32_t zconst_h2 = h2_bcast(__float2half_rn(p.zero_const));
-    const int group = GROUP > 0 ? GROUP : (GROUP == 0 ? p.k : p.group);
-    const int lane_k = t * (G::kFrag / 4);
-    const int blk = blk0 + warp;
-    const bool active = blk < n_blocks;
-    const uint32_t half_sel = (t >> 1) ? 0x3232u : 0x1010u;  // which of two packed groups a lane pair uses
+    return;
+  }
 
-    float acc[MT][2][4];
+  // -------------------------------------------------------------- consumer warps
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const ZeroConsts zc = make_zero_consts(ZMODE, p.zero_const);
+  const uint32_t zconst_h2 = h2_bcast(__float2half_rn(p.zero_const));
+  const int group = GROUP > 0 ? GROUP : (GROUP == 0 ? p.k : p.group);
+  const int lane_k = t * (G::kFrag / 4);
+  const uint32_t half_sel = (t >> 1) ? 0x3232u : 0x1010u;  // which of two packed groups a lane pair uses
+
+  float acc[MT][2][4];
+  uint32_t s_cur[SP::kCount], s_nxt[SP::kCount];
+  uint32_t z_cur[SP::kCount], z_nxt[SP::kCount];
+
+  int stage = 0;
+  uint32_t phase = 0;
+  int round = 0;        // tiles this cluster has finished
+  int leads_done = 0;   // tiles this CTA has led
+  bool ok = true;
+
+  for (int tile = cluster_id; tile < n_tiles && ok; tile += n_clusters, ++round) {
+    const int blk = tile * kConsumerWarps + warp;
+    const bool active = blk < n_blocks;
 #pragma unroll
     for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -209,8 +267,6 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][c][j] = 0.0f;
 
-    uint32_t s_cur[SP::kCount], s_nxt[SP::kCount];
-    uint32_t z_cur[SP::kCount], z_nxt[SP::kCount];
     auto fetch_global = [&](int chunk_i, uint32_t (&sv)[SP::kCount], uint32_t (&zv)[SP::kCount]) {
       if (SRC != kSrcGlobal || !active) return;
       const int64_t n_g = (int64_t)blk * 16 + g;
@@ -225,12 +281,9 @@ __global__ void __launch_bounds__(kThreads, 2)
         if (ZMODE == kZeroGeneral) zv[i] = p.z ? (ld_nc_u16(p.z + o_g) | (ld_nc_u16(p.z + o_g8) << 16)) : 0u;
       }
     };
-
-    int stage = 0;
-    uint32_t phase = 0;
     if (c0 < c1) fetch_global(c0, s_nxt, z_nxt);
-    bool ok = true;
-    for (int chunk = c0; chunk < c1 && ok; ++chunk) {
+
+    for (int chunk = c0; chunk < c1; ++chunk) {
       if (SRC == kSrcGlobal) {
 #pragma unroll
         for (int i = 0; i < SP::kCount; ++i) {
@@ -344,6 +397,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         phase ^= 1u;
       }
     }
+    if (!ok) break;
 
     // fold the two chains
 #pragma unroll
@@ -351,27 +405,48 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[mt][0][c] += acc[mt][1][c];
 
+    bool store = (S == 1);
     if (S > 1) {
-      // publish this CTA's partial fragments for the cluster's first CTA
-      float* dst = red + (size_t)warp * MT * 128 + lane;
+      const int buf = round & 1;
+      const int leader = round % S;
+      // my buffer `buf` was last used for tile round-2: its leader must have summed it
+      if (round >= 2) {
+        if (!mbar_wait_cluster_bounded(&free_bar[buf], (uint32_t)(((round >> 1) - 1) & 1), p.status)) {
+          ok = false;
+          break;
+        }
+      }
+      float* dst = red + (size_t)buf * kRedFloats + (size_t)warp * MT * 128 + lane;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) dst[mt * 128 + c * 32] = acc[mt][0][c];
-    }
-    __syncwarp();
-    if (S > 1) cluster_sync_all();
-    if (rank == 0 && active) {
-      if (S > 1) {
-        const uint32_t base = smem_u32(red + (size_t)warp * MT * 128 + lane);
-        for (int r = 1; r < S; ++r) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(ready_bar), (uint32_t)leader));
+      if (rank == leader) {
+        if (!mbar_wait_cluster_bounded(ready_bar, (uint32_t)(leads_done & 1), p.status)) {
+          ok = false;
+          break;
+        }
+        ++leads_done;
+        const uint32_t base = smem_u32(red + (size_t)buf * kRedFloats + (size_t)warp * MT * 128 + lane);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[mt][0][c] = 0.0f;
+        for (int r = 0; r < S; ++r) {  // fixed rank order: deterministic
           const uint32_t ra = map_to_rank(base, (uint32_t)r);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[mt][0][c] += ld_dsmem_f32(ra + (mt * 128 + c * 32) * 4);
         }
+        __syncwarp();
+        if (lane < S) mbar_arrive_remote(map_to_rank(smem_u32(&free_bar[buf]), (uint32_t)lane));
+        store = true;
       }
+    }
+    if (store && active) {
       const int64_t n0 = (int64_t)blk * 16 + g;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
@@ -383,15 +458,12 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
       }
     }
-    __syncwarp();
-    if (S > 1) cluster_sync_all();  // partials stay readable until the first CTA has summed them
-    return;
   }
-  // producer warp takes part in both cluster barriers
-  __syncwarp();
-  if (S > 1) {
-    cluster_sync_all();
-    cluster_sync_all();
+
+  // nobody leaves while a leader may still read its partials: wait for the last hand-backs
+  if (S > 1 && ok) {
+    for (int r = max(0, round - 2); r < round; ++r)
+      mbar_wait_cluster_bounded(&free_bar[r & 1], (uint32_t)((r >> 1) & 1), p.status);
   }
 }
 
@@ -399,8 +471,12 @@ __global__ void __launch_bounds__(kThreads, 2)
 
 struct ClusterLaunch {
   int bits, mt, zmode, group_code, src;
-  int grid, split;
-  size_t smem_bytes;
+  int n_tiles, cpt, sm_count;
+  int ctas_per_sm;      // residency target used to size the pipeline
+  int force_split;      // > 0: use this split factor (diagnostics)
+  int force_stages;     // > 0: use this many pipeline stages (diagnostics)
+  size_t stage_bytes;   // one pipeline stage
+  size_t fixed_bytes;   // partial-fragment buffers
 };
 
 // implemented per bit width (two translation units, so they compile in parallel)

@@ -1,0 +1,604 @@
+// Decode-path kernel on the 5th-generation tensor cores (tcgen05 + TMEM), int4 weights, m <= 32.
+//
+// Why not mma.sync: on B200 the legacy warp MMA issues about once per 32 clocks per SM
+// sub-partition, so a 16 x 16 weight fragment costs as many MMAs as there are 8-row batch tiles
+// and the decode path turns MMA-bound from m = 9 upward (and latency-bound below).  Here the
+// dequantised weights are the A operand of tcgen05.mma and live in tensor memory; the batch is
+// the MMA's N (16 or 32), so one instruction covers 128 weight rows x 16 k for the whole batch.
+//
+//   producer warp  : bulk async copies of the 16 KB packed-weight slice of a (128-row tile,
+//                    256-k chunk) + TMA tiles of x (128B-swizzled K-major) and of the scales
+//                    into a ring of shared-memory stages
+//   8 decode warps : thread = one weight row = one TMEM lane; reads its row's packed nibbles
+//                    from the fragment-ordered stage, decodes them bit-exactly (lop3 + exact
+//                    .rn fp16 ops), writes 64 k of fp16 into a TMEM A buffer with tcgen05.st
+//   MMA warp       : one thread issues 4 x tcgen05.mma (M=128, N=16|32, K=16) per 64-k block,
+//                    A from TMEM, B = x tile from shared memory, fp32 accumulators in TMEM;
+//                    tcgen05.commit recycles A buffers and stages
+//   epilogue       : the decode warps read the accumulator with tcgen05.ld, apply bias /
+//                    activation / residual, round once to fp16 and store.
+//
+// Work split (stream-k): the (tile, chunk) iteration space is cut into equal contiguous ranges,
+// one per persistent CTA.  A CTA computes first the pieces of tiles it shares with neighbours:
+// the tail piece (tile started by an earlier CTA) goes to a global fp32 slot + epoch flag
+// straight away; the head piece (tile this CTA owns) stays in TMEM; then all whole tiles; at
+// the very end the owner adds the other CTAs' slots - written long before, so the bounded flag
+// wait does not block in practice - and stores.  Sum order is fixed (CTA order): deterministic.
+//
+// Stands in for fastertransformer::gemm_fp16_int_bias_act[_residual] at small m
+// (python/tvm/contrib/cutlass/gemm_operation.py:441-458) and the reference's GEMV /
+// LowBatchGEMV schedules (python/tvm/dlight/gpu/gemv.py:216-530, low_batch_gemv.py:300-613).
+#pragma once
+
+#include <cuda.h>
+
+#include "dequant.cuh"
+#include "gemv.h"
+
+namespace rb200 {
+namespace ug {
+
+constexpr int kDecodeWarps = 8;                 // two groups of four (one group = 128 TMEM lanes)
+constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr int kTileRows = 128;
+constexpr int kKBlock = 64;                     // k per MMA block (4 x K=16) and per fragment tile
+constexpr int kBlocksPerChunk = 4;              // 256 k per stage
+constexpr int kChunk = kKBlock * kBlocksPerChunk;
+constexpr int kWBlockPitch = 2048 + 16;         // 16-row block slice of a stage, +16 B against bank conflicts
+constexpr int kWBytes = ((8 * kWBlockPitch + 127) / 128) * 128;
+constexpr int kScaleBoxBytes = 2048;
+constexpr int kNumA = 4;                        // TMEM A buffers (32 columns each)
+constexpr int kNumD = 3;                        // accumulators: two for whole tiles, one for the owned piece
+constexpr int kTmemCols = 256;
+
+enum ScaleSrc : int { kSrcGlobal = 0, kSrcSmemNK = 1, kSrcSmemKN = 2 };
+
+struct Params {
+  GemvParams g;
+  float* partial;        // [grid][nb][128] fp32 tail pieces
+  unsigned* flags;       // [grid][4] epoch flags, one per lane quadrant
+  unsigned epoch;
+  int nb;                // MMA N: 16 or 32 (batch rows padded)
+  int has_z_tile;
+  unsigned s_box_bytes;
+};
+
+struct Layout {
+  int x_bytes;      // nb * 128 * 4 sub-tiles
+  int w_off, s_off, z_off, stage_bytes;
+};
+inline Layout make_layout(int nb, int src, int zmode) {
+  Layout l;
+  l.x_bytes = nb * 128 * kBlocksPerChunk;
+  l.w_off = l.x_bytes;
+  l.s_off = l.w_off + kWBytes;
+  l.z_off = l.s_off + (src != kSrcGlobal ? kScaleBoxBytes : 0);
+  int end = l.z_off + ((src != kSrcGlobal && zmode == kZeroGeneral) ? kScaleBoxBytes : 0);
+  l.stage_bytes = ((end + 1023) / 1024) * 1024;
+  return l;
+}
+
+#ifdef __CUDACC__
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]; kind::f16, fp32 accumulate
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B apart
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                              // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ long long range_start(long long cta, long long total, long long grid) {
+  return cta * total / grid;
+}
+
+// A piece of work: chunks [c0, c1) of `tile`; where the accumulator goes afterwards.
+enum PieceKind : int { kWhole = 0, kTail = 1, kHead = 2 };
+struct Piece {
+  int tile, c0, c1, kind, dbuf;
+};
+
+// Enumerates the pieces of CTA `cta` in execution order: tail piece, head piece, whole tiles.
+// Returns false when idx is past the end.  All warps of the CTA call this with the same idx.
+__device__ __forceinline__ bool get_piece(long long it0, long long it1, int cpt, int idx, Piece* pc) {
+  if (it0 >= it1) return false;
+  const int first_tile = (int)(it0 / cpt), last_tile = (int)((it1 - 1) / cpt);
+  const int fc0 = (int)(it0 % cpt);
+  const int lc1 = (int)((it1 - 1) % cpt) + 1;
+  // does the range begin mid-tile (tail piece of a tile owned by an earlier CTA)?
+  const bool has_tail = fc0 != 0;
+  // does it end mid-tile while having started that tile at chunk 0 (head piece of an owned tile)?
+  const bool single = first_tile == last_tile;
+  const bool has_head = lc1 != cpt && !(single && has_tail);
+  int n = 0;
+  if (has_tail) {
+    if (idx == n) {
+      pc->tile = first_tile;
+      pc->c0 = fc0;
+      pc->c1 = single ? lc1 : cpt;
+      pc->kind = kTail;
+      pc->dbuf = 0;
+      return true;
+    }
+    ++n;
+  }
+  if (has_head) {
+    if (idx == n) {
+      pc->tile = last_tile;
+      pc->c0 = 0;
+      pc->c1 = lc1;
+      pc->kind = kHead;
+      pc->dbuf = 2;
+      return true;
+    }
+    ++n;
+  }
+  const int w0 = first_tile + (has_tail ? 1 : 0);
+  const int w1 = last_tile - ((has_head || (single && has_tail)) ? 1 : 0);  // inclusive
+  const int wi = idx - n;
+  if (w0 + wi <= w1) {
+    pc->tile = w0 + wi;
+    pc->c0 = 0;
+    pc->c1 = cpt;
+    pc->kind = kWhole;
+    pc->dbuf = wi & 1;
+    return true;
+  }
+  return false;
+}
+
+template <int ZMODE, int GROUP, int SRC>
+__global__ void __launch_bounds__(kThreads, 2)
+    umma_gemv_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_x,
+                     const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_z) {
+  extern __shared__ uint8_t smem_raw[];
+  const GemvParams& p = pp.g;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int nb = pp.nb;
+  const int stages = p.stages;
+  const int x_bytes = nb * 128 * kBlocksPerChunk;
+  const int w_off = x_bytes;
+  const int s_off = w_off + kWBytes;
+  const int z_off = s_off + (SRC != kSrcGlobal ? kScaleBoxBytes : 0);
+  const int stage_bytes =
+      ((z_off + ((SRC != kSrcGlobal && ZMODE == kZeroGeneral) ? kScaleBoxBytes : 0) + 1023) / 1024) * 1024;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
+  uint64_t* stage_full = bars;
+  uint64_t* stage_empty = stage_full + stages;
+  uint64_t* a_full = stage_empty + stages;
+  uint64_t* a_empty = a_full + kNumA;
+  uint64_t* d_full = a_empty + kNumA;
+  uint64_t* d_empty = d_full + kNumD;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_empty + kNumD);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&stage_full[s], 1);
+      mbar_init(&stage_empty[s], kDecodeWarps + 1);
+    }
+    for (int i = 0; i < kNumA; ++i) {
+      mbar_init(&a_full[i], 4);
+      mbar_init(&a_empty[i], 1);
+    }
+    for (int i = 0; i < kNumD; ++i) {
+      mbar_init(&d_full[i], 1);
+      mbar_init(&d_empty[i], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t d_col0 = tmem_base;                  // kNumD accumulators of nb columns
+  const uint32_t a_col0 = tmem_base + kNumD * 32;     // kNumA buffers of 32 columns
+
+  const long long total = p.total_iters;
+  const long long grid = gridDim.x;
+  const long long it0 = range_start(blockIdx.x, total, grid);
+  const long long it1 = range_start(blockIdx.x + 1, total, grid);
+  const int cpt = p.chunks_per_tile;
+  const int kb_total = p.k / kKBlock;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ============================================================ producer
+    int stage = 0;
+    uint32_t phase = 0;
+    Piece pc;
+    for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
+      const int blk0 = pc.tile * 8;
+      for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
+        if (!mbar_wait_bounded(&stage_empty[stage], phase ^ 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        const int kb0 = chunk * kBlocksPerChunk;
+        const int nkb = min(kBlocksPerChunk, kb_total - kb0);
+        uint8_t* sbase = smem + (size_t)stage * stage_bytes;
+        const uint32_t wbytes = (uint32_t)nkb * 512;
+        uint32_t tx = wbytes * 8 + (uint32_t)nkb * nb * 128;
+        if (SRC != kSrcGlobal) tx += pp.s_box_bytes * (pp.has_z_tile ? 2u : 1u);
+        if (lane == 0) mbar_arrive_expect_tx(&stage_full[stage], tx);
+        __syncwarp();
+        if (lane < 8) {
+          const uint8_t* src = p.w + ((size_t)(blk0 + lane) * kb_total + kb0) * 512;
+          bulk_g2s(sbase + w_off + lane * kWBlockPitch, src, wbytes, &stage_full[stage]);
+        } else if (lane < 8 + nkb) {
+          const int j = lane - 8;  // x sub-tile: [nb rows][64 k], 128B swizzle
+          tma_load_2d(sbase + j * nb * 128, &tmap_x, (kb0 + j) * kKBlock, 0, &stage_full[stage]);
+        } else if (SRC != kSrcGlobal && lane == 12) {
+          constexpr int kGroupsPerChunk = GROUP > 0 ? (kChunk / GROUP) : 1;
+          const int gc0 = chunk * kGroupsPerChunk;
+          if (SRC == kSrcSmemNK) tma_load_2d(sbase + s_off, &tmap_s, gc0, blk0 * 16, &stage_full[stage]);
+          else tma_load_2d(sbase + s_off, &tmap_s, blk0 * 16, gc0, &stage_full[stage]);
+        } else if (SRC != kSrcGlobal && ZMODE == kZeroGeneral && lane == 13 && pp.has_z_tile) {
+          constexpr int kGroupsPerChunk = GROUP > 0 ? (kChunk / GROUP) : 1;
+          const int gc0 = chunk * kGroupsPerChunk;
+          if (SRC == kSrcSmemNK) tma_load_2d(sbase + z_off, &tmap_z, gc0, blk0 * 16, &stage_full[stage]);
+          else tma_load_2d(sbase + z_off, &tmap_z, blk0 * 16, gc0, &stage_full[stage]);
+        }
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer (one thread)
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(nb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t q = 0;  // running 64-k block counter (selects the A buffer)
+      uint32_t d_uses[kNumD] = {0, 0, 0};
+      Piece pc;
+      for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
+        const int db = pc.dbuf;
+        if (!mbar_wait_bounded(&d_empty[db], (d_uses[db] & 1u) ^ 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        ++d_uses[db];
+        tc_fence_after();
+        const uint32_t d_tmem = d_col0 + db * 32;
+        bool first = true;
+        for (int chunk = pc.c0; ok && chunk < pc.c1; ++chunk) {
+          if (!mbar_wait_bounded(&stage_full[stage], phase, p.status)) {
+            ok = false;
+            break;
+          }
+          const int kb0 = chunk * kBlocksPerChunk;
+          const int nkb = min(kBlocksPerChunk, kb_total - kb0);
+          const uint32_t xbase = smem_u32(smem + (size_t)stage * stage_bytes);
+          for (int kb = 0; kb < nkb; ++kb, ++q) {
+            const uint32_t ab = q % kNumA;
+            if (!mbar_wait_bounded(&a_full[ab], (q / kNumA) & 1u, p.status)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_tmem = a_col0 + ab * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t bdesc = make_b_desc(xbase + kb * nb * 128 + j * 32);
+              tc_mma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
+            }
+            first = false;
+            tc_commit(&a_empty[ab]);
+          }
+          tc_commit(&stage_empty[stage]);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        tc_commit(&d_full[db]);
+      }
+    }
+  } else {
+    // ============================================================ decode + epilogue warps
+    const int dw = warp - 2;
+    const int grp = dw >> 2;             // which half of the 64-k blocks this warp decodes
+    const int w4 = warp & 3;             // TMEM lane quadrant of this warp
+    const int hi = w4 & 1;               // rows g (0) or g+8 (1) of the 16-row blocks
+    const int bl = (w4 >> 1) * 4 + (lane & 3);  // 16-row block inside the tile
+    const int g = lane >> 2;
+    const int row = 16 * bl + g + 8 * hi;       // weight row inside the tile held by this TMEM lane
+    const uint32_t lane_taddr = (uint32_t)(32 * w4) << 16;
+    const ZeroConsts zc = make_zero_consts(ZMODE, p.zero_const);
+    const uint32_t zconst_h2 = h2_bcast(__float2half_rn(p.zero_const));
+    const int group = GROUP > 0 ? GROUP : (GROUP == 0 ? p.k : p.group);
+    const uint32_t nib_mask = hi ? 0x00f000f0u : 0x000f000fu;
+    constexpr uint32_t kMagic = 0x64006400u, kSixteenth = 0x2C002C00u;
+
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t q = 0;
+    uint32_t d_uses[kNumD] = {0, 0, 0};
+    float owned[32];  // not used: the owned piece stays in TMEM (d buffer 2)
+    (void)owned;
+    Piece pc;
+    bool have_head = false;
+    int head_tile = 0;
+    for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
+      const int64_t n_row = (int64_t)pc.tile * kTileRows + row;
+      uint32_t s_chan = 0, z_chan = zconst_h2;
+      if (GROUP == 0) {
+        s_chan = h2_bcast(p.s[n_row * p.s_n]);
+        if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row * p.s_n]);
+      }
+      for (int chunk = pc.c0; ok && chunk < pc.c1; ++chunk) {
+        if (!mbar_wait_bounded(&stage_full[stage], phase, p.status)) {
+          ok = false;
+          break;
+        }
+        const int kb0 = chunk * kBlocksPerChunk;
+        const int nkb = min(kBlocksPerChunk, kb_total - kb0);
+        const uint8_t* sbase = smem + (size_t)stage * stage_bytes;
+        const uint8_t* wrow = sbase + w_off + bl * kWBlockPitch + g * 64;
+        uint4 nk_s = make_uint4(0, 0, 0, 0), nk_z = make_uint4(0, 0, 0, 0);
+        if (SRC == kSrcSmemNK) {
+          nk_s = *reinterpret_cast<const uint4*>(sbase + s_off + row * 16);
+          if (ZMODE == kZeroGeneral && pp.has_z_tile) nk_z = *reinterpret_cast<const uint4*>(sbase + z_off + row * 16);
+        }
+        for (int kb = 0; kb < nkb; ++kb, ++q) {
+          if ((int)(q & 1u) != grp) continue;  // the other group's block
+          const uint32_t ab = q % kNumA;
+          if (!mbar_wait_bounded(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t regs[32];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const uint4 u = *reinterpret_cast<const uint4*>(wrow + kb * 512 + t * 16);
+            // scale / zero of this 16-k run
+            uint32_t s2, z2 = zconst_h2;
+            if (GROUP == 0) {
+              s2 = s_chan;
+              z2 = z_chan;
+            } else if (SRC == kSrcSmemNK) {
+              // group 32: run t of block kb is group 2kb + t/2 of the chunk
+              const int gi = 2 * kb + (t >> 1);
+              const uint32_t wsel = (gi >> 1) == 0 ? nk_s.x : ((gi >> 1) == 1 ? nk_s.y : ((gi >> 1) == 2 ? nk_s.z : nk_s.w));
+              s2 = prmt(wsel, wsel, (gi & 1) ? 0x3232u : 0x1010u);
+              if (ZMODE == kZeroGeneral && pp.has_z_tile) {
+                const uint32_t zsel = (gi >> 1) == 0 ? nk_z.x : ((gi >> 1) == 1 ? nk_z.y : ((gi >> 1) == 2 ? nk_z.z : nk_z.w));
+                z2 = prmt(zsel, zsel, (gi & 1) ? 0x3232u : 0x1010u);
+              }
+            } else if (SRC == kSrcSmemKN) {
+              const int gl = (kb * kKBlock + t * 16) / (GROUP > 0 ? GROUP : 1);
+              s2 = h2_bcast(reinterpret_cast<const __half*>(sbase + s_off)[gl * kTileRows + row]);
+              if (ZMODE == kZeroGeneral && pp.has_z_tile)
+                z2 = h2_bcast(reinterpret_cast<const __half*>(sbase + z_off)[gl * kTileRows + row]);
+            } else {
+              const int64_t kk = (int64_t)(kb0 + kb) * kKBlock + t * 16;
+              const int64_t o = n_row * p.s_n + (kk / group) * p.s_g;
+              s2 = h2_bcast(p.s[o]);
+              if (ZMODE == kZeroGeneral && p.z) z2 = h2_bcast(p.z[o]);
+            }
+            const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t e0 = and_or(ww[j], nib_mask, kMagic);
+              uint32_t e1 = and_or(ww[j] >> 8, nib_mask, kMagic);
+              if (hi) {
+                e0 = h2_fma(e0, kSixteenth, zc.add_hi);
+                e1 = h2_fma(e1, kSixteenth, zc.add_hi);
+              } else {
+                e0 = h2_sub(e0, zc.sub_lo);
+                e1 = h2_sub(e1, zc.sub_lo);
+              }
+              if (ZMODE == kZeroGeneral) {
+                e0 = h2_sub(e0, z2);
+                e1 = h2_sub(e1, z2);
+              }
+              regs[8 * t + 2 * j] = h2_mul(e0, s2);
+              regs[8 * t + 2 * j + 1] = h2_mul(e1, s2);
+            }
+          }
+          tc_st32(lane_taddr | (a_col0 + ab * 32), regs);
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[ab]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stage_empty[stage]);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok) break;
+      // ---------------------------------------------------------- accumulator hand-over
+      const int db = pc.dbuf;
+      if (pc.kind == kHead) {  // stays in TMEM until the fix-up at the end
+        have_head = true;
+        head_tile = pc.tile;
+        ++d_uses[db];
+        continue;
+      }
+      // one group drains a given accumulator: tail pieces and even whole tiles group 0, odd group 1
+      const int drain_grp = (pc.kind == kWhole) ? (db & 1) : 0;
+      const uint32_t use = d_uses[db]++;
+      if (grp != drain_grp) continue;
+      if (!mbar_wait_bounded(&d_full[db], use & 1u, p.status)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_taddr = lane_taddr | (d_col0 + db * 32);
+      const int64_t n_out = (int64_t)pc.tile * kTileRows + row;
+      for (int c0 = 0; c0 < nb; c0 += 16) {
+        float v[16];
+        tc_ld16(d_taddr + c0, v);
+        if (pc.kind == kTail) {
+          float* dst = pp.partial + ((size_t)blockIdx.x * nb + c0) * kTileRows + row;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) dst[(size_t)i * kTileRows] = v[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c0 + i;
+            if (m < p.m) p.out[(int64_t)m * p.ldo + n_out] = __float2half_rn(apply_epilogue(v[i], p.epi, m, n_out));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&d_empty[db]);
+      if (pc.kind == kTail) {
+        // publish per warp: the owner's lane quadrant w4 reads exactly the rows this warp wrote
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_u32(pp.flags + blockIdx.x * 4 + w4, pp.epoch);
+      }
+    }
+
+    // ------------------------------------------------------------ fix-up of the owned tile
+    if (ok && have_head && grp == 1) {
+      const int db = 2;
+      if (mbar_wait_bounded(&d_full[db], 0u, p.status)) {
+        tc_fence_after();
+        // contributors: the CTAs after this one whose range reaches into head_tile
+        const long long hi_it = (long long)head_tile * cpt + cpt - 1;
+        const int last_cta = (int)(((hi_it + 1) * grid - 1) / total);
+        const uint32_t d_taddr = lane_taddr | (d_col0 + db * 32);
+        const int64_t n_out = (int64_t)head_tile * kTileRows + row;
+        bool flags_ok = true;
+        for (int c = blockIdx.x + 1; c <= last_cta && flags_ok; ++c) {
+          const long long t0 = clock64();
+          while (ld_acquire_u32(pp.flags + c * 4 + w4) != pp.epoch) {
+            if (clock64() - t0 > (1ll << 31)) {
+              if (p.status) atomicExch(p.status, kStatusWaitTimeout);
+              flags_ok = false;
+              break;
+            }
+          }
+        }
+        if (flags_ok) {
+          for (int c0 = 0; c0 < nb; c0 += 16) {
+            float v[16];
+            tc_ld16(d_taddr + c0, v);
+            for (int c = blockIdx.x + 1; c <= last_cta; ++c) {
+              const float* src = pp.partial + ((size_t)c * nb + c0) * kTileRows + row;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] += __ldcg(src + (size_t)i * kTileRows);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int m = c0 + i;
+              if (m < p.m) p.out[(int64_t)m * p.ldo + n_out] = __float2half_rn(apply_epilogue(v[i], p.epi, m, n_out));
+            }
+          }
+        }
+        tc_fence_before();
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace ug
+
+// Host entry: plans and launches the tcgen05 decode kernel.  Returns 1 when the problem is
+// outside what this kernel covers (caller falls back to the warp-MMA kernel), 0 on launch,
+// -1 on error.
+int umma_gemv_run(const GemvParams& p, int bits, int zmode, int sm_count, float* partial,
+                  size_t partial_bytes, unsigned* flags, size_t flag_count, unsigned epoch,
+                  cudaStream_t stream);
+
+}  // namespace rb200
