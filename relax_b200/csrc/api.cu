@@ -95,7 +95,7 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ w, const __half* _
   for (int64_t tile = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5); tile < tiles;
        tile += (int64_t)gridDim.x * (blockDim.x >> 5)) {
     const int64_t nb = tile / KB, kb = tile % KB;
-    const uint4 wv = reinterpret_cast<const uint4*>(w)[tile * 32 + lane];
+    const uint4 wv = reinterpret_cast<const uint4*>(w)[tile * 32 + frag_unit_pos(lane)];
     const int64_t n_g = nb * 16 + g;
     const int64_t k0 = kb * kFrag + t * (kFrag / 4);
     const int64_t grp = k0 / group;
@@ -287,6 +287,12 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
+#ifdef RB200_ABLATE
+    {
+      const char* ab = getenv("RB200_GEMV_ABLATE");
+      p.ablate = ab ? atoi(ab) : 0;
+    }
+#endif
     {
       // tensor-core (tcgen05) decode kernel where it applies; epoch flags live past the ticket area
       constexpr size_t kFlagOffset = 49152, kFlagCount = 16384;

@@ -101,6 +101,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// Same, for roles with slack (producer, MMA issuer): sleeps between polls so the waiting warp
+// does not take issue slots from the warps doing the arithmetic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      __nanosleep(40);
+    }
+    if (clock64() - t0 > (1ll << 31)) {
+      if (status) atomicExch(status, kStatusWaitTimeout);
+      return false;
+    }
+  }
+}
+
 // 1-D bulk async copy global -> shared, completion counted on an mbarrier (both addresses and
 // the size must be multiples of 16 bytes).
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes,

@@ -11,8 +11,12 @@
 // Fragment layout (what rb200_preprocess_weight writes).  The weight of one expert is a grid of
 // 512-byte tiles, tile (nb, kb) at byte offset (nb * KB + kb) * 512 where nb indexes 16 output
 // rows and kb indexes KFRAG reduction elements (KFRAG = 64 for int4, 32 for int8, KB = K/KFRAG).
-// Inside a tile lane L (0..31) owns bytes [16L, 16L+16); with g = L >> 2, t = L & 3 those 16
-// bytes hold rows {g, g+8} of the 16-row block and the reduction elements
+// Inside a tile the 16-byte unit of "lane" L = 4g + t (g = 0..7, t = 0..3) sits at byte
+// 16 * unit_pos(L), unit_pos = 8t + ((g + 2t) & 7): all g of one t share a 128-byte line (what a
+// quarter-warp of the tensor-core decode kernel reads at once) and the units of lanes 8q..8q+7
+// fall in eight different 16-byte bank groups (what a quarter-warp of the warp-MMA kernels
+// reads at once), so neither access pattern has shared-memory bank conflicts.  The unit holds
+// rows {g, g+8} of the 16-row block and the reduction elements
 //   int4: k = 64*kb + 16*t + [0,16)     int8: k = 32*kb + 8*t + [0,8)
 //   int4 word j (0..3) covers k4 = 4j..4j+3; nibble p of the word holds
 //        p=0:(g,k4+0) p=4:(g,k4+1) p=2:(g,k4+2) p=6:(g,k4+3)
@@ -36,6 +40,12 @@ struct Epilogue {
   int64_t ld_res;
   int act, binop, unop;
 };
+
+// Position (in 16-byte units) of lane L's unit inside a 512-byte fragment tile.
+__host__ __device__ __forceinline__ int frag_unit_pos(int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  return 8 * t + ((g + 2 * t) & 7);
+}
 
 #ifdef __CUDACC__
 

@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
 #pragma unroll
       for (int kb = 0; kb < kBlocksPerChunk; ++kb) {
         if (kb < nkb) {
-          const uint4 wv = wsm[kb * 32 + lane];
+          const uint4 wv = wsm[kb * 32 + frag_unit_pos(lane)];
           constexpr int si_div = SP::kSpan / G::kFrag;  // fragment tiles per fetched scale
           const uint32_t sp = s_cur[kb / si_div];
           const uint32_t s_g = prmt(sp, sp, 0x1010u);

@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
         for (int kb = 0; kb < kBlocksPerChunk; ++kb) {
           if (kb < nkb) {
-            const uint4 wv = wsm[kb * 32 + lane];
+            const uint4 wv = wsm[kb * 32 + frag_unit_pos(lane)];
             uint32_t s_g, s_g8, z_g = zconst_h2, z_g8 = zconst_h2;
             if (SRC == kSrcGlobal) {
               constexpr int si_div = SP::kSpan / G::kFrag;

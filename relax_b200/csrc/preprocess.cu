@@ -2,7 +2,7 @@
 // Stands in for fastertransformer::preprocess_weights as called by
 // cutlass.ft_preprocess_weight (src/runtime/contrib/cutlass/weight_preprocess.cc:38-58): same
 // byte size in and out, signed codes biased to unsigned, layout private to the matmul kernels.
-#include "common.cuh"
+#include "dequant.cuh"
 #include "preprocess.h"
 
 namespace rb200 {
@@ -68,7 +68,7 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
           words[2 * j + r8] = w;
         }
     }
-    reinterpret_cast<uint4*>(dst + e * expert_bytes)[r] = make_uint4(words[0], words[1], words[2], words[3]);
+    reinterpret_cast<uint4*>(dst + e * expert_bytes)[tile * 32 + frag_unit_pos(lane)] = make_uint4(words[0], words[1], words[2], words[3]);
   }
 }
 

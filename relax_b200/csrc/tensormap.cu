@@ -12,10 +12,7 @@ EncodeFn g_encode = nullptr;
 std::once_flag g_once;
 }  // namespace
 
-int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype,
-                       unsigned long long dim0, unsigned long long dim1,
-                       unsigned long long stride1_bytes, unsigned box0, unsigned box1,
-                       CUtensorMapSwizzle swizzle) {
+static int resolve_encode() {
   std::call_once(g_once, [] {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -24,16 +21,42 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType d
       g_encode = reinterpret_cast<EncodeFn>(fn);
   });
   RB200_CHECK(g_encode != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
-  RB200_CHECK((reinterpret_cast<uintptr_t>(base) & 15u) == 0 && stride1_bytes % 16 == 0,
-              "tensor map needs a 16-byte aligned base and row pitch (pitch %llu)", stride1_bytes);
-  cuuint64_t dims[2] = {dim0, dim1};
-  cuuint64_t strides[1] = {stride1_bytes};
-  cuuint32_t box[2] = {box0, box1};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+  return 0;
+}
+
+int make_tensor_map(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int rank,
+                    const unsigned long long* dims, const unsigned long long* strides_bytes,
+                    const unsigned* box, CUtensorMapSwizzle swizzle) {
+  if (resolve_encode() != 0) return -1;
+  RB200_CHECK(rank >= 1 && rank <= 5, "tensor map rank %d out of range", rank);
+  RB200_CHECK((reinterpret_cast<uintptr_t>(base) & 15u) == 0, "tensor map needs a 16-byte aligned base");
+  cuuint64_t d[5];
+  cuuint64_t st[4];
+  cuuint32_t bx[5];
+  cuuint32_t es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) {
+      RB200_CHECK(strides_bytes[i] % 16 == 0, "tensor map pitch %llu is not a multiple of 16", strides_bytes[i]);
+      st[i] = strides_bytes[i];
+    }
+  }
+  CUresult r = g_encode(out, dtype, (cuuint32_t)rank, const_cast<void*>(base), d, st, bx, es,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RB200_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return 0;
+}
+
+int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype,
+                       unsigned long long dim0, unsigned long long dim1,
+                       unsigned long long stride1_bytes, unsigned box0, unsigned box1,
+                       CUtensorMapSwizzle swizzle) {
+  const unsigned long long dims[2] = {dim0, dim1};
+  const unsigned long long strides[1] = {stride1_bytes};
+  const unsigned box[2] = {box0, box1};
+  return make_tensor_map(out, base, dtype, 2, dims, strides, box, swizzle);
 }
 }  // namespace rb200

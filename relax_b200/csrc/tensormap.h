@@ -12,4 +12,8 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType d
                        unsigned long long dim0, unsigned long long dim1,
                        unsigned long long stride1_bytes, unsigned box0, unsigned box1,
                        CUtensorMapSwizzle swizzle);
+// General form: rank 1..5, dims[0] innermost, strides_bytes[i] = pitch of dims[i+1].
+int make_tensor_map(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int rank,
+                    const unsigned long long* dims, const unsigned long long* strides_bytes,
+                    const unsigned* box, CUtensorMapSwizzle swizzle);
 }  // namespace rb200

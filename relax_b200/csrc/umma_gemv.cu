@@ -10,8 +10,8 @@ namespace rb200 {
 namespace ug {
 
 template <int ZMODE, int GROUP, int SRC>
-int launch_inst(const Params& pp, int grid, size_t smem, const CUtensorMap& tx, const CUtensorMap& ts,
-                const CUtensorMap& tz, cudaStream_t stream) {
+int launch_inst(const Params& pp, int grid, size_t smem, const CUtensorMap& tw, const CUtensorMap& tx,
+                const CUtensorMap& ts, const CUtensorMap& tz, cudaStream_t stream) {
   auto kern = umma_gemv_kernel<ZMODE, GROUP, SRC>;
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -20,16 +20,16 @@ int launch_inst(const Params& pp, int grid, size_t smem, const CUtensorMap& tx, 
     RB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured_device = dev;
   }
-  kern<<<grid, kThreads, smem, stream>>>(pp, tx, ts, tz);
+  kern<<<grid, kThreads, smem, stream>>>(pp, tw, tx, ts, tz);
   RB200_CUDA(cudaGetLastError());
   return 0;
 }
 
 template <int ZMODE>
-int launch_gs(int group_code, int src, const Params& pp, int grid, size_t smem, const CUtensorMap& tx,
-              const CUtensorMap& ts, const CUtensorMap& tz, cudaStream_t stream) {
+int launch_gs(int group_code, int src, const Params& pp, int grid, size_t smem, const CUtensorMap& tw,
+              const CUtensorMap& tx, const CUtensorMap& ts, const CUtensorMap& tz, cudaStream_t stream) {
 #define RB200_CASE(G, S) \
-  if (group_code == (G) && src == (S)) return launch_inst<ZMODE, G, S>(pp, grid, smem, tx, ts, tz, stream)
+  if (group_code == (G) && src == (S)) return launch_inst<ZMODE, G, S>(pp, grid, smem, tw, tx, ts, tz, stream)
   RB200_CASE(32, kSrcGlobal);
   RB200_CASE(64, kSrcGlobal);
   RB200_CASE(128, kSrcGlobal);
@@ -80,12 +80,22 @@ int umma_gemv_run(const GemvParams& p_in, int bits, int zmode, int sm_count, flo
     else if (p.s_n == 1 && p.s_g == p.n && kChunk % p.group == 0) src = kSrcSmemKN;
   }
 
-  CUtensorMap tx, ts, tz;
+  CUtensorMap tw, tx, ts, tz;
   memset(&ts, 0, sizeof(ts));
-  if (make_tensor_map_2d(&tx, p.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (unsigned long long)p.k,
-                         (unsigned long long)p.m, (unsigned long long)p.ldx * 2, kKBlock, (unsigned)pp.nb,
-                         CU_TENSOR_MAP_SWIZZLE_128B) != 0)
-    return -1;
+  {
+    // weight as [N/16 row blocks][K*8 bytes] in 8-byte elements; box = 8 blocks x 2 KB
+    const unsigned long long kb_total = (unsigned long long)p.k / kKBlock;
+    if (make_tensor_map_2d(&tw, p.w, CU_TENSOR_MAP_DATA_TYPE_UINT64, kb_total * 64, (unsigned long long)p.n / 16,
+                           kb_total * 512, 256, 8, CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
+      return -1;
+    // x as {64 k, m rows, K/64 blocks}: a box of 4 blocks lands as four 128B-swizzled K-major tiles
+    const unsigned long long dims[3] = {(unsigned long long)kKBlock, (unsigned long long)p.m, kb_total};
+    const unsigned long long strides[2] = {(unsigned long long)p.ldx * 2, (unsigned long long)kKBlock * 2};
+    const unsigned box[3] = {(unsigned)kKBlock, (unsigned)pp.nb, (unsigned)kBlocksPerChunk};
+    if (make_tensor_map(&tx, p.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+      return -1;
+  }
   ts = tx;
   tz = tx;
   if (src == kSrcSmemNK) {
@@ -121,13 +131,13 @@ int umma_gemv_run(const GemvParams& p_in, int bits, int zmode, int sm_count, flo
   p.total_iters = (long long)cpt * n_tiles;
   static const int env_stages = getenv("RB200_GEMV_STAGES") ? atoi(getenv("RB200_GEMV_STAGES")) : 0;
   static const int env_grid = getenv("RB200_GEMV_GRID") ? atoi(getenv("RB200_GEMV_GRID")) : 0;
-  long long grid = (long long)sm_count * 2;
+  long long grid = (long long)sm_count * 2;  // two persistent CTAs per SM, half the tensor memory each
   if (env_grid > 0) grid = env_grid;
   if (grid > p.total_iters) grid = p.total_iters;
 
   const Layout lay = make_layout(pp.nb, src, zmode);
   const size_t fixed = 1024 /* alignment slack */ + (size_t)(2 * 16 + 2 * kNumA + 2 * kNumD) * sizeof(uint64_t) + 16;
-  const size_t budget = (size_t)(228 * 1024) / 2 - 1024;
+  const size_t budget = (size_t)(228 * 1024) / 2 - 1024 - 512;
   int stages = (int)((budget - fixed) / lay.stage_bytes);
   if (env_stages > 0) stages = env_stages;
   if (stages > 16) stages = 16;
@@ -143,8 +153,8 @@ int umma_gemv_run(const GemvParams& p_in, int bits, int zmode, int sm_count, flo
   pp.epoch = epoch;
 
   if (zmode == kZeroConstInt)
-    return launch_gs<kZeroConstInt>(group_code, src, pp, (int)grid, smem, tx, ts, tz, stream);
-  return launch_gs<kZeroGeneral>(group_code, src, pp, (int)grid, smem, tx, ts, tz, stream);
+    return launch_gs<kZeroConstInt>(group_code, src, pp, (int)grid, smem, tw, tx, ts, tz, stream);
+  return launch_gs<kZeroGeneral>(group_code, src, pp, (int)grid, smem, tw, tx, ts, tz, stream);
 }
 
 }  // namespace rb200

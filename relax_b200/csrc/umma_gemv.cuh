@@ -6,15 +6,21 @@
 // dequantised weights are the A operand of tcgen05.mma and live in tensor memory; the batch is
 // the MMA's N (16 or 32), so one instruction covers 128 weight rows x 16 k for the whole batch.
 //
-//   producer warp  : bulk async copies of the 16 KB packed-weight slice of a (128-row tile,
-//                    256-k chunk) + TMA tiles of x (128B-swizzled K-major) and of the scales
-//                    into a ring of shared-memory stages
-//   8 decode warps : thread = one weight row = one TMEM lane; reads its row's packed nibbles
-//                    from the fragment-ordered stage, decodes them bit-exactly (lop3 + exact
-//                    .rn fp16 ops), writes 64 k of fp16 into a TMEM A buffer with tcgen05.st
-//   MMA warp       : one thread issues 4 x tcgen05.mma (M=128, N=16|32, K=16) per 64-k block,
-//                    A from TMEM, B = x tile from shared memory, fp32 accumulators in TMEM;
-//                    tcgen05.commit recycles A buffers and stages
+//   producer warp  : three TMA tile loads per (128-row tile, 256-k chunk) into a ring of
+//                    shared-memory stages - the 16 KB packed-weight slice (8 row blocks x 2 KB,
+//                    one 2-D box over the fragment-ordered weight), the x slice (128B-swizzled
+//                    K-major, one 3-D box) and the scale tile.  Few large loads per stage:
+//                    issuing a dozen small copies per stage capped the pipeline at ~3 TB/s
+//   8 decode warps : two groups of four warps; group i takes the blocks 2h + i of every chunk
+//                    (h = 0, 1).  thread = one weight row = one TMEM lane; reads its row's packed
+//                    nibbles from the fragment-ordered stage, decodes them bit-exactly (lop3 +
+//                    exact .rn fp16 ops), writes 64 k of fp16 into its quarter of a TMEM A buffer
+//                    with tcgen05.st
+//   MMA warp       : one thread waits once per half chunk and issues 8 x tcgen05.mma (M=128,
+//                    N=16|32, K=16), A from TMEM, B = x tile from shared memory, fp32
+//                    accumulators in TMEM; tcgen05.commit recycles A buffers and stages
+//                    (hand-offs per 128 k, not per 64-k block, to keep the single issuing
+//                    thread off the critical path)
 //   epilogue       : the decode warps read the accumulator with tcgen05.ld, apply bias /
 //                    activation / residual, round once to fp16 and store.
 //
@@ -44,12 +50,14 @@ constexpr int kTileRows = 128;
 constexpr int kKBlock = 64;                     // k per MMA block (4 x K=16) and per fragment tile
 constexpr int kBlocksPerChunk = 4;              // 256 k per stage
 constexpr int kChunk = kKBlock * kBlocksPerChunk;
-constexpr int kWBlockPitch = 2048 + 16;         // 16-row block slice of a stage, +16 B against bank conflicts
-constexpr int kWBytes = ((8 * kWBlockPitch + 127) / 128) * 128;
+constexpr int kWBlockPitch = 2048;              // 16-row block slice of a stage (4 fragment tiles)
+constexpr int kWBytes = 8 * kWBlockPitch;
 constexpr int kScaleBoxBytes = 2048;
-constexpr int kNumA = 4;                        // TMEM A buffers (32 columns each)
+constexpr int kNumA = 2;                        // TMEM A buffers, half a chunk (two 64-k blocks, 64 columns) each
+constexpr int kACols = 64;
 constexpr int kNumD = 3;                        // accumulators: two for whole tiles, one for the owned piece
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 256;                  // half the tensor memory: two CTAs per SM (one CTA alone
+                                                // cannot pull more than ~4.4 TB/s through its copy pipeline)
 
 enum ScaleSrc : int { kSrcGlobal = 0, kSrcSmemNK = 1, kSrcSmemKN = 2 };
 
@@ -87,6 +95,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
           smem_u32(smem_dst)),
       "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t cols) {
@@ -220,10 +236,101 @@ __device__ __forceinline__ bool get_piece(long long it0, long long it1, int cpt,
   return false;
 }
 
+// Decodes one 64-k block (fragment tile KB of the chunk) of this thread's weight row into 32
+// packed fp16 pairs.  HI (rows g+8 of the 16-row block: high nibbles) and KB are compile-time so
+// that masks, shared-memory offsets and scale selectors fold into immediates.
+struct RowCtx {
+  const uint8_t* wblk;     // this thread's 16-row block inside the stage
+  uint32_t unit_off[4];    // byte offset of unit (g, t) inside a fragment tile
+  const uint8_t* s_tile;   // staged scale tile (or nullptr)
+  const uint8_t* z_tile;
+  uint4 nk_s, nk_z;        // kSrcSmemNK: this row's 8 group scales / zeros of the chunk
+  uint32_t s_chan, z_chan; // GROUP == 0
+  int row;
+  int64_t n_row;
+  int kb0;
+};
+
+template <int ZMODE, int GROUP, int SRC, int HI, int KB>
+__device__ __forceinline__ void decode_block(const GemvParams& p, const Params& pp, const RowCtx& c,
+                                             const ZeroConsts& zc, uint32_t zconst_h2, int group,
+                                             uint32_t (&regs)[32]) {
+  constexpr uint32_t kMagic = 0x64006400u, kSixteenth = 0x2C002C00u;
+  constexpr uint32_t kMask = HI ? 0x00f000f0u : 0x000f000fu;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const uint4 u = *reinterpret_cast<const uint4*>(c.wblk + KB * 512 + c.unit_off[t]);
+    uint32_t s2, z2 = zconst_h2;
+    if (GROUP == 0) {
+      s2 = c.s_chan;
+      z2 = c.z_chan;
+    } else if (SRC == kSrcSmemNK) {
+      constexpr int gi = 2 * KB;  // group 32: runs t = 0,1 -> group 2KB, t = 2,3 -> group 2KB + 1
+      const uint32_t wsel = (gi >> 1) == 0 ? c.nk_s.x : ((gi >> 1) == 1 ? c.nk_s.y : ((gi >> 1) == 2 ? c.nk_s.z : c.nk_s.w));
+      s2 = prmt(wsel, wsel, (t >> 1) ? 0x3232u : 0x1010u);
+      if (ZMODE == kZeroGeneral && pp.has_z_tile) {
+        const uint32_t zsel = (gi >> 1) == 0 ? c.nk_z.x : ((gi >> 1) == 1 ? c.nk_z.y : ((gi >> 1) == 2 ? c.nk_z.z : c.nk_z.w));
+        z2 = prmt(zsel, zsel, (t >> 1) ? 0x3232u : 0x1010u);
+      }
+    } else if (SRC == kSrcSmemKN) {
+      constexpr int kG = GROUP > 0 ? GROUP : 1;
+      const int gl = (KB * kKBlock + t * 16) / kG;
+      s2 = h2_bcast(reinterpret_cast<const __half*>(c.s_tile)[gl * kTileRows + c.row]);
+      if (ZMODE == kZeroGeneral && pp.has_z_tile)
+        z2 = h2_bcast(reinterpret_cast<const __half*>(c.z_tile)[gl * kTileRows + c.row]);
+    } else {
+      const int64_t kk = (int64_t)(c.kb0 + KB) * kKBlock + t * 16;
+      const int64_t o = c.n_row * p.s_n + (kk / group) * p.s_g;
+      s2 = h2_bcast(p.s[o]);
+      if (ZMODE == kZeroGeneral && p.z) z2 = h2_bcast(p.z[o]);
+    }
+    const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t e0 = and_or(ww[j], kMask, kMagic);
+      uint32_t e1 = and_or(ww[j] >> 8, kMask, kMagic);
+      if (HI) {
+        e0 = h2_fma(e0, kSixteenth, zc.add_hi);
+        e1 = h2_fma(e1, kSixteenth, zc.add_hi);
+      } else {
+        e0 = h2_sub(e0, zc.sub_lo);
+        e1 = h2_sub(e1, zc.sub_lo);
+      }
+      if (ZMODE == kZeroGeneral) {
+        e0 = h2_sub(e0, z2);
+        e1 = h2_sub(e1, z2);
+      }
+      regs[8 * t + 2 * j] = h2_mul(e0, s2);
+      regs[8 * t + 2 * j + 1] = h2_mul(e1, s2);
+    }
+  }
+}
+
+template <int ZMODE, int GROUP, int SRC, int HI>
+__device__ __forceinline__ void decode_block_kb(int kb, const GemvParams& p, const Params& pp, const RowCtx& c,
+                                                const ZeroConsts& zc, uint32_t zconst_h2, int group,
+                                                uint32_t (&regs)[32]) {
+  switch (kb) {
+    case 0:
+      decode_block<ZMODE, GROUP, SRC, HI, 0>(p, pp, c, zc, zconst_h2, group, regs);
+      break;
+    case 1:
+      decode_block<ZMODE, GROUP, SRC, HI, 1>(p, pp, c, zc, zconst_h2, group, regs);
+      break;
+    case 2:
+      decode_block<ZMODE, GROUP, SRC, HI, 2>(p, pp, c, zc, zconst_h2, group, regs);
+      break;
+    default:
+      decode_block<ZMODE, GROUP, SRC, HI, 3>(p, pp, c, zc, zconst_h2, group, regs);
+      break;
+  }
+}
+
 template <int ZMODE, int GROUP, int SRC>
 __global__ void __launch_bounds__(kThreads, 2)
-    umma_gemv_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_x,
-                     const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_z) {
+    umma_gemv_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_w,
+                     const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_s,
+                     const __grid_constant__ CUtensorMap tmap_z) {
   extern __shared__ uint8_t smem_raw[];
   const GemvParams& p = pp.g;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -255,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(&stage_empty[s], kDecodeWarps + 1);
     }
     for (int i = 0; i < kNumA; ++i) {
-      mbar_init(&a_full[i], 4);
+      mbar_init(&a_full[i], kDecodeWarps);
       mbar_init(&a_empty[i], 1);
     }
     for (int i = 0; i < kNumD; ++i) {
@@ -272,13 +379,18 @@ __global__ void __launch_bounds__(kThreads, 2)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t d_col0 = tmem_base;                  // kNumD accumulators of nb columns
-  const uint32_t a_col0 = tmem_base + kNumD * 32;     // kNumA buffers of 32 columns
+  const uint32_t a_col0 = tmem_base;                  // kNumA buffers of kACols columns
+  const uint32_t d_col0 = tmem_base + kNumA * kACols; // kNumD accumulators of up to 32 columns
 
   const long long total = p.total_iters;
   const long long grid = gridDim.x;
+#ifdef RB200_ABLATE
+  const int ablate = p.ablate;
+#else
+  constexpr int ablate = 0;
+#endif
   const long long it0 = range_start(blockIdx.x, total, grid);
-  const long long it1 = range_start(blockIdx.x + 1, total, grid);
+  const long long it1 = (ablate & 8) ? it0 : range_start(blockIdx.x + 1, total, grid);
   const int cpt = p.chunks_per_tile;
   const int kb_total = p.k / kKBlock;
   bool ok = true;
@@ -291,25 +403,35 @@ __global__ void __launch_bounds__(kThreads, 2)
     for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
       const int blk0 = pc.tile * 8;
       for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
-        if (!mbar_wait_bounded(&stage_empty[stage], phase ^ 1u, p.status)) {
+        if ((ablate & 2048) ? !mbar_wait_bounded(&stage_empty[stage], phase ^ 1u, p.status)
+                            : !mbar_wait_relaxed(&stage_empty[stage], phase ^ 1u, p.status)) {
           ok = false;
           break;
         }
         const int kb0 = chunk * kBlocksPerChunk;
         const int nkb = min(kBlocksPerChunk, kb_total - kb0);
         uint8_t* sbase = smem + (size_t)stage * stage_bytes;
-        const uint32_t wbytes = (uint32_t)nkb * 512;
-        uint32_t tx = wbytes * 8 + (uint32_t)nkb * nb * 128;
-        if (SRC != kSrcGlobal) tx += pp.s_box_bytes * (pp.has_z_tile ? 2u : 1u);
+        // every load delivers its full box (out-of-range parts arrive as zeros)
+        uint32_t tx = (uint32_t)kWBytes;
+        if (!(ablate & 16)) tx += (uint32_t)kBlocksPerChunk * nb * 128;
+        if (SRC != kSrcGlobal && !(ablate & 32)) tx += pp.s_box_bytes * (pp.has_z_tile ? 2u : 1u);
         if (lane == 0) mbar_arrive_expect_tx(&stage_full[stage], tx);
         __syncwarp();
-        if (lane < 8) {
-          const uint8_t* src = p.w + ((size_t)(blk0 + lane) * kb_total + kb0) * 512;
-          bulk_g2s(sbase + w_off + lane * kWBlockPitch, src, wbytes, &stage_full[stage]);
-        } else if (lane < 8 + nkb) {
-          const int j = lane - 8;  // x sub-tile: [nb rows][64 k], 128B swizzle
-          tma_load_2d(sbase + j * nb * 128, &tmap_x, (kb0 + j) * kKBlock, 0, &stage_full[stage]);
-        } else if (SRC != kSrcGlobal && lane == 12) {
+        (void)nkb;
+        if (ablate & 128) {
+          if (lane >= 16 && lane < 24) {
+            const int b = lane - 16;
+            const uint8_t* src = p.w + ((size_t)(blk0 + b) * kb_total + kb0) * 512;
+            bulk_g2s(sbase + w_off + b * kWBlockPitch, src, 2048, &stage_full[stage]);
+          }
+        }
+        if (lane == 0 && !(ablate & 128)) {
+          // weight: rows = 16-row blocks, inner = that block's bytes in 8-byte elements
+          tma_load_2d(sbase + w_off, &tmap_w, kb0 * 64, blk0, &stage_full[stage]);
+        } else if (lane == 1 && !(ablate & 16)) {
+          // x: {k inside a 64-block, batch row, 64-block} -> four [nb rows][64 k] sub-tiles, 128B swizzle
+          tma_load_3d(sbase, &tmap_x, 0, 0, kb0, &stage_full[stage]);
+        } else if (SRC != kSrcGlobal && lane == 12 && !(ablate & 32)) {
           constexpr int kGroupsPerChunk = GROUP > 0 ? (kChunk / GROUP) : 1;
           const int gc0 = chunk * kGroupsPerChunk;
           if (SRC == kSrcSmemNK) tma_load_2d(sbase + s_off, &tmap_s, gc0, blk0 * 16, &stage_full[stage]);
@@ -332,12 +454,12 @@ __global__ void __launch_bounds__(kThreads, 2)
       const uint32_t idesc = (1u << 4) | ((uint32_t)(nb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t q = 0;  // running 64-k block counter (selects the A buffer)
+      uint32_t q = 0;  // running chunk counter (selects the A buffer)
       uint32_t d_uses[kNumD] = {0, 0, 0};
       Piece pc;
       for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
         const int db = pc.dbuf;
-        if (!mbar_wait_bounded(&d_empty[db], (d_uses[db] & 1u) ^ 1u, p.status)) {
+        if (!mbar_wait_relaxed(&d_empty[db], (d_uses[db] & 1u) ^ 1u, p.status)) {
           ok = false;
           break;
         }
@@ -346,28 +468,42 @@ __global__ void __launch_bounds__(kThreads, 2)
         const uint32_t d_tmem = d_col0 + db * 32;
         bool first = true;
         for (int chunk = pc.c0; ok && chunk < pc.c1; ++chunk) {
-          if (!mbar_wait_bounded(&stage_full[stage], phase, p.status)) {
+          if (!((ablate & 4096) ? mbar_wait_bounded(&stage_full[stage], phase, p.status) : mbar_wait_relaxed(&stage_full[stage], phase, p.status))) {
             ok = false;
             break;
           }
           const int kb0 = chunk * kBlocksPerChunk;
           const int nkb = min(kBlocksPerChunk, kb_total - kb0);
           const uint32_t xbase = smem_u32(smem + (size_t)stage * stage_bytes);
-          for (int kb = 0; kb < nkb; ++kb, ++q) {
+          for (int h = 0; h < 2; ++h, ++q) {
             const uint32_t ab = q % kNumA;
-            if (!mbar_wait_bounded(&a_full[ab], (q / kNumA) & 1u, p.status)) {
+            if (!(ablate & 256) && !((ablate & 4096) ? mbar_wait_bounded(&a_full[ab], (q / kNumA) & 1u, p.status) : mbar_wait_relaxed(&a_full[ab], (q / kNumA) & 1u, p.status))) {
               ok = false;
               break;
             }
             tc_fence_after();
-            const uint32_t a_tmem = a_col0 + ab * 32;
+            for (int kb = 2 * h; kb < min(nkb, 2 * h + 2); ++kb) {
+              const uint32_t a_tmem = a_col0 + ab * kACols + (kb & 1) * 32;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint64_t bdesc = make_b_desc(xbase + kb * nb * 128 + j * 32);
-              tc_mma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
+              for (int j = 0; j < 4; ++j) {
+                if ((ablate & 4) && !(first && j == 0)) continue;
+                const uint64_t bdesc = make_b_desc(xbase + kb * nb * 128 + j * 32);
+                tc_mma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
+              }
+              first = false;
             }
-            first = false;
-            tc_commit(&a_empty[ab]);
+            if (ablate & 256) {
+            } else if (ablate & 64) mbar_arrive(&a_empty[ab]);
+            else tc_commit(&a_empty[ab]);
+          }
+          if (!ok) break;
+          if (ablate & 64) {
+            if (!(ablate & 512)) mbar_arrive(&stage_empty[stage]);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
           }
           tc_commit(&stage_empty[stage]);
           if (++stage == stages) {
@@ -381,18 +517,19 @@ __global__ void __launch_bounds__(kThreads, 2)
   } else {
     // ============================================================ decode + epilogue warps
     const int dw = warp - 2;
-    const int grp = dw >> 2;             // which half of the 64-k blocks this warp decodes
+    const int grp = dw >> 2;             // which 64-k block of every chunk this warp decodes
     const int w4 = warp & 3;             // TMEM lane quadrant of this warp
     const int hi = w4 & 1;               // rows g (0) or g+8 (1) of the 16-row blocks
-    const int bl = (w4 >> 1) * 4 + (lane & 3);  // 16-row block inside the tile
-    const int g = lane >> 2;
+    const int bl = (w4 >> 1) * 4 + (lane >> 3);  // 16-row block inside the tile
+    const int g = lane & 7;
     const int row = 16 * bl + g + 8 * hi;       // weight row inside the tile held by this TMEM lane
     const uint32_t lane_taddr = (uint32_t)(32 * w4) << 16;
     const ZeroConsts zc = make_zero_consts(ZMODE, p.zero_const);
     const uint32_t zconst_h2 = h2_bcast(__float2half_rn(p.zero_const));
     const int group = GROUP > 0 ? GROUP : (GROUP == 0 ? p.k : p.group);
-    const uint32_t nib_mask = hi ? 0x00f000f0u : 0x000f000fu;
-    constexpr uint32_t kMagic = 0x64006400u, kSixteenth = 0x2C002C00u;
+    uint32_t unit_off[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) unit_off[t] = (uint32_t)(t * 128 + ((g + 2 * t) & 7) * 16);
 
     int stage = 0;
     uint32_t phase = 0;
@@ -418,77 +555,54 @@ __global__ void __launch_bounds__(kThreads, 2)
         const int kb0 = chunk * kBlocksPerChunk;
         const int nkb = min(kBlocksPerChunk, kb_total - kb0);
         const uint8_t* sbase = smem + (size_t)stage * stage_bytes;
-        const uint8_t* wrow = sbase + w_off + bl * kWBlockPitch + g * 64;
-        uint4 nk_s = make_uint4(0, 0, 0, 0), nk_z = make_uint4(0, 0, 0, 0);
+        RowCtx c;
+        c.wblk = sbase + w_off + bl * kWBlockPitch;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) c.unit_off[t] = unit_off[t];
+        c.s_tile = sbase + s_off;
+        c.z_tile = sbase + z_off;
+        c.nk_s = make_uint4(0, 0, 0, 0);
+        c.nk_z = make_uint4(0, 0, 0, 0);
         if (SRC == kSrcSmemNK) {
-          nk_s = *reinterpret_cast<const uint4*>(sbase + s_off + row * 16);
-          if (ZMODE == kZeroGeneral && pp.has_z_tile) nk_z = *reinterpret_cast<const uint4*>(sbase + z_off + row * 16);
+          c.nk_s = *reinterpret_cast<const uint4*>(sbase + s_off + row * 16);
+          if (ZMODE == kZeroGeneral && pp.has_z_tile) c.nk_z = *reinterpret_cast<const uint4*>(sbase + z_off + row * 16);
         }
-        for (int kb = 0; kb < nkb; ++kb, ++q) {
-          if ((int)(q & 1u) != grp) continue;  // the other group's block
+        c.s_chan = s_chan;
+        c.z_chan = z_chan;
+        c.row = row;
+        c.n_row = n_row;
+        c.kb0 = kb0;
+        for (int h = 0; h < 2 && ok; ++h, ++q) {
           const uint32_t ab = q % kNumA;
-          if (!mbar_wait_bounded(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
+          if (!(ablate & 256) && !mbar_wait_bounded(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          uint32_t regs[32];
+          const int kb = 2 * h + grp;
+          if (kb < nkb) {
+            uint32_t regs[32];
+            if (ablate & 1) {
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const uint4 u = *reinterpret_cast<const uint4*>(wrow + kb * 512 + t * 16);
-            // scale / zero of this 16-k run
-            uint32_t s2, z2 = zconst_h2;
-            if (GROUP == 0) {
-              s2 = s_chan;
-              z2 = z_chan;
-            } else if (SRC == kSrcSmemNK) {
-              // group 32: run t of block kb is group 2kb + t/2 of the chunk
-              const int gi = 2 * kb + (t >> 1);
-              const uint32_t wsel = (gi >> 1) == 0 ? nk_s.x : ((gi >> 1) == 1 ? nk_s.y : ((gi >> 1) == 2 ? nk_s.z : nk_s.w));
-              s2 = prmt(wsel, wsel, (gi & 1) ? 0x3232u : 0x1010u);
-              if (ZMODE == kZeroGeneral && pp.has_z_tile) {
-                const uint32_t zsel = (gi >> 1) == 0 ? nk_z.x : ((gi >> 1) == 1 ? nk_z.y : ((gi >> 1) == 2 ? nk_z.z : nk_z.w));
-                z2 = prmt(zsel, zsel, (gi & 1) ? 0x3232u : 0x1010u);
-              }
-            } else if (SRC == kSrcSmemKN) {
-              const int gl = (kb * kKBlock + t * 16) / (GROUP > 0 ? GROUP : 1);
-              s2 = h2_bcast(reinterpret_cast<const __half*>(sbase + s_off)[gl * kTileRows + row]);
-              if (ZMODE == kZeroGeneral && pp.has_z_tile)
-                z2 = h2_bcast(reinterpret_cast<const __half*>(sbase + z_off)[gl * kTileRows + row]);
+              for (int t = 0; t < 32; ++t) regs[t] = 0x3c003c00u;
+            } else if (hi) {
+              decode_block_kb<ZMODE, GROUP, SRC, 1>(kb, p, pp, c, zc, zconst_h2, group, regs);
             } else {
-              const int64_t kk = (int64_t)(kb0 + kb) * kKBlock + t * 16;
-              const int64_t o = n_row * p.s_n + (kk / group) * p.s_g;
-              s2 = h2_bcast(p.s[o]);
-              if (ZMODE == kZeroGeneral && p.z) z2 = h2_bcast(p.z[o]);
+              decode_block_kb<ZMODE, GROUP, SRC, 0>(kb, p, pp, c, zc, zconst_h2, group, regs);
             }
-            const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t e0 = and_or(ww[j], nib_mask, kMagic);
-              uint32_t e1 = and_or(ww[j] >> 8, nib_mask, kMagic);
-              if (hi) {
-                e0 = h2_fma(e0, kSixteenth, zc.add_hi);
-                e1 = h2_fma(e1, kSixteenth, zc.add_hi);
-              } else {
-                e0 = h2_sub(e0, zc.sub_lo);
-                e1 = h2_sub(e1, zc.sub_lo);
-              }
-              if (ZMODE == kZeroGeneral) {
-                e0 = h2_sub(e0, z2);
-                e1 = h2_sub(e1, z2);
-              }
-              regs[8 * t + 2 * j] = h2_mul(e0, s2);
-              regs[8 * t + 2 * j + 1] = h2_mul(e1, s2);
+            if (!(ablate & 2)) {
+              tc_st32(lane_taddr | (a_col0 + ab * kACols + grp * 32), regs);
+              tc_wait_st();
             }
           }
-          tc_st32(lane_taddr | (a_col0 + ab * 32), regs);
-          tc_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&a_full[ab]);
+          if (lane == 0 && !(ablate & 256)) mbar_arrive(&a_full[ab]);
         }
+        if (!ok) break;
         __syncwarp();
         if (lane == 0) mbar_arrive(&stage_empty[stage]);
+        if ((ablate & 512) && warp == 2 && lane == 0) mbar_arrive(&stage_empty[stage]);
         if (++stage == stages) {
           stage = 0;
           phase ^= 1u;
@@ -503,7 +617,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         ++d_uses[db];
         continue;
       }
-      // one group drains a given accumulator: tail pieces and even whole tiles group 0, odd group 1
+      // one group drains a given accumulator: whole tiles alternate, tail pieces group 0
       const int drain_grp = (pc.kind == kWhole) ? (db & 1) : 0;
       const uint32_t use = d_uses[db]++;
       if (grp != drain_grp) continue;

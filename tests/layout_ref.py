@@ -4,6 +4,20 @@ relax_b200/csrc/dequant.cuh, independently of the CUDA repack kernel."""
 import numpy as np
 
 
+def unit_pos(lane: int) -> int:
+    """16-byte unit position of lane 4g+t inside a 512-byte tile: 8t + ((g + 2t) & 7)."""
+    g, t = lane >> 2, lane & 3
+    return 8 * t + ((g + 2 * t) & 7)
+
+
+def _place_units(tiles: np.ndarray) -> np.ndarray:
+    """tiles[..., lane, unit payload] -> same shape with lane's unit moved to unit_pos(lane)."""
+    out = np.empty_like(tiles)
+    for lane in range(32):
+        out[..., unit_pos(lane), :] = tiles[..., lane, :]
+    return out
+
+
 def fragment_layout(codes: np.ndarray, bits: int) -> np.ndarray:
     """codes uint8 [N, K] (unsigned) -> uint8 flat array of N*K*bits/8 bytes."""
     n, k = codes.shape
@@ -17,11 +31,12 @@ def fragment_layout(codes: np.ndarray, bits: int) -> np.ndarray:
         for r2 in range(2):
             for cc in range(4):
                 words |= c[:, r2, :, :, :, :, cc] << np.uint32(4 * slot[r2, cc])
-        # memory order: nb, kb, lane = g*4 + t, j
-        out = words.transpose(0, 2, 1, 3, 4).reshape(-1)
-        return out.astype("<u4").view(np.uint8)
+        # memory order: nb, kb, unit position of lane (g, t), j
+        tiles = words.transpose(0, 2, 1, 3, 4).reshape(n // 16, kb, 32, 4)  # [nb, kb, lane=4g+t, j]
+        return _place_units(tiles).reshape(-1).astype("<u4").view(np.uint8)
     kb = k // 32
     # [nb, r2, g, kb, t, j, c] with k = kb*32 + t*8 + j*4 + c
     c = codes.reshape(n // 16, 2, 8, kb, 4, 2, 4)
-    # memory order: nb, kb, g, t, j, r2, c
-    return np.ascontiguousarray(c.transpose(0, 3, 2, 4, 5, 1, 6)).reshape(-1).astype(np.uint8)
+    # memory order: nb, kb, unit position of lane (g, t), then (j, r2, c) inside the 16-byte unit
+    tiles = np.ascontiguousarray(c.transpose(0, 3, 2, 4, 5, 1, 6)).reshape(n // 16, kb, 32, 16)
+    return _place_units(tiles).reshape(-1).astype(np.uint8)
