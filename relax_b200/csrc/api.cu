@@ -95,7 +95,7 @@ __global__ void dequantize_kernel(const uint8_t* __restrict__ w, const __half* _
   for (int64_t tile = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5); tile < tiles;
        tile += (int64_t)gridDim.x * (blockDim.x >> 5)) {
     const int64_t nb = tile / KB, kb = tile % KB;
-    const uint4 wv = reinterpret_cast<const uint4*>(w)[tile * 32 + frag_unit_pos(lane)];
+    const uint4 wv = reinterpret_cast<const uint4*>(w + frag_tile_offset(nb, kb, N / 16, KB))[frag_unit_pos(lane)];
     const int64_t n_g = nb * 16 + g;
     const int64_t k0 = kb * kFrag + t * (kFrag / 4);
     const int64_t grp = k0 / group;

@@ -8,9 +8,15 @@
 // with one correctly rounded fp16 subtraction; the product is one correctly rounded fp16
 // multiply.  Every fp16 op is issued as explicit ".rn" PTX so the compiler cannot contract.
 //
-// Fragment layout (what rb200_preprocess_weight writes).  The weight of one expert is a grid of
-// 512-byte tiles, tile (nb, kb) at byte offset (nb * KB + kb) * 512 where nb indexes 16 output
-// rows and kb indexes KFRAG reduction elements (KFRAG = 64 for int4, 32 for int8, KB = K/KFRAG).
+// Fragment layout (what rb200_preprocess_weight writes).  The weight of one expert is a set of
+// 512-byte fragment tiles; tile (nb, kb) covers 16 output rows (row block nb) x KFRAG reduction
+// elements (KFRAG = 64 for int4, 32 for int8; KB = K / KFRAG, NB = N / 16).  Tiles are ordered so
+// that everything one pipeline stage of the matmul kernels needs - 8 row blocks (128 rows) x 4
+// k-blocks - is ONE contiguous 16 KB run (the copy engine pays per contiguous segment, not per
+// byte: eight 2 KB segments per stage halve the streaming rate of an SM):
+//     offset(nb, kb) = ((t * 8 * KB) + c * 4 * nblk(t) + b * nkb(c) + j) * 512
+//     t = nb / 8, b = nb % 8, c = kb / 4, j = kb % 4,
+//     nblk(t) = min(8, NB - 8t)  (last row tile may be short),  nkb(c) = min(4, KB - 4c).
 // Inside a tile the 16-byte unit of "lane" L = 4g + t (g = 0..7, t = 0..3) sits at byte
 // 16 * unit_pos(L), unit_pos = 8t + ((g + 2t) & 7): all g of one t share a 128-byte line (what a
 // quarter-warp of the tensor-core decode kernel reads at once) and the units of lanes 8q..8q+7
@@ -40,6 +46,18 @@ struct Epilogue {
   int64_t ld_res;
   int act, binop, unop;
 };
+
+// Byte offset of fragment tile (nb, kb) inside one expert's weight, and of the contiguous run
+// that holds all tiles of (row tile t, k-chunk c).
+__host__ __device__ __forceinline__ int64_t frag_stage_offset(int64_t t, int64_t c, int64_t NB, int64_t KB) {
+  const int64_t nblk = (NB - 8 * t) < 8 ? (NB - 8 * t) : 8;
+  return (t * 8 * KB + c * 4 * nblk) * 512;
+}
+__host__ __device__ __forceinline__ int64_t frag_tile_offset(int64_t nb, int64_t kb, int64_t NB, int64_t KB) {
+  const int64_t t = nb >> 3, b = nb & 7, c = kb >> 2, j = kb & 3;
+  const int64_t nkb = (KB - 4 * c) < 4 ? (KB - 4 * c) : 4;
+  return frag_stage_offset(t, c, NB, KB) + (b * nkb + j) * 512;
+}
 
 // Position (in 16-byte units) of lane L's unit inside a 512-byte fragment tile.
 __host__ __device__ __forceinline__ int frag_unit_pos(int lane) {

@@ -111,13 +111,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
       const int blk0 = (int)tile * kConsumerWarps;
       const int nblk = min(kConsumerWarps, n_blocks - blk0);
       uint8_t* sbase = smem + (size_t)stage * kStage;
-      const uint32_t wbytes = (uint32_t)nkb * kTileBytes;
+      const uint32_t wbytes = (uint32_t)nkb * kTileBytes * nblk;  // one contiguous run per stage
       const uint32_t xbytes = (uint32_t)nkb * G::kFrag * 2;
-      if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], wbytes * nblk + xbytes * p.m);
+      if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], wbytes + xbytes * p.m);
       __syncwarp();
-      if (lane < nblk) {
-        const uint8_t* src = p.w + ((size_t)(blk0 + lane) * kb_total + kb0) * kTileBytes;
-        bulk_g2s(sbase + lane * (kBlocksPerChunk * kTileBytes), src, wbytes, &full_bar[stage]);
+      if (lane == 0) {
+        const uint8_t* src = p.w + frag_stage_offset(tile, chunk, n_blocks, kb_total);
+        bulk_g2s(sbase, src, wbytes, &full_bar[stage]);
       }
       for (int r = lane; r < p.m; r += 32) {
         const __half* src = p.x + (size_t)r * p.ldx + (size_t)kb0 * G::kFrag;
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     const int blk = (int)tile * kConsumerWarps + warp;
     const uint8_t* sbase = smem + (size_t)stage * kStage;
     if (blk < n_blocks && !(ablate & 4)) {
-      const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * (kBlocksPerChunk * kTileBytes));
+      const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * (nkb * kTileBytes));
       const uint8_t* xsm = sbase + G::kWBytes + g * G::kXPitch + t * (G::kFrag / 2);
 #pragma unroll
       for (int kb = 0; kb < kBlocksPerChunk; ++kb) {

@@ -202,15 +202,15 @@ __global__ void __launch_bounds__(kThreads, 2)
         const int kb0 = chunk * kBlocksPerChunk;
         const int nkb = min(kBlocksPerChunk, kb_total - kb0);
         uint8_t* sbase = smem + (size_t)stage * kStage;
-        const uint32_t wbytes = (uint32_t)nkb * kTileBytes;
+        const uint32_t wbytes = (uint32_t)nkb * kTileBytes * nblk;  // one contiguous run per stage
         const uint32_t xbytes = (uint32_t)nkb * G::kFrag * 2;
-        uint32_t tx = wbytes * nblk + xbytes * p.m;
+        uint32_t tx = wbytes + xbytes * p.m;
         if (SRC != kSrcGlobal) tx += cp.s_box_bytes * (cp.has_z_tile ? 2u : 1u);
         if (lane == 0) mbar_arrive_expect_tx(&full_bar[stage], tx);
         __syncwarp();
-        if (lane < nblk) {
-          const uint8_t* src = p.w + ((size_t)(blk0 + lane) * kb_total + kb0) * kTileBytes;
-          bulk_g2s(sbase + lane * (kBlocksPerChunk * kTileBytes), src, wbytes, &full_bar[stage]);
+        if (lane == 0) {
+          const uint8_t* src = p.w + frag_stage_offset(tile, chunk, n_blocks, kb_total);
+          bulk_g2s(sbase, src, wbytes, &full_bar[stage]);
         }
         if (SRC != kSrcGlobal) {
           // coordinates: NK tensor {group, row}; KN tensor {row, group}
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       const int nkb = min(kBlocksPerChunk, kb_total - kb0);
       const uint8_t* sbase = smem + (size_t)stage * kStage;
       if (active) {
-        const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * (kBlocksPerChunk * kTileBytes));
+        const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * (nkb * kTileBytes));
         const uint8_t* xsm = sbase + G::kWBytes + g * G::kXPitch + t * (G::kFrag / 2);
         // staged scale rows of this lane (kSrcSmemNK: 8 groups of rows g and g+8)
         uint4 nk_s_g, nk_s_g8, nk_z_g, nk_z_g8;

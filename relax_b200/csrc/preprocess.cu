@@ -68,7 +68,7 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
           words[2 * j + r8] = w;
         }
     }
-    reinterpret_cast<uint4*>(dst + e * expert_bytes)[tile * 32 + frag_unit_pos(lane)] = make_uint4(words[0], words[1], words[2], words[3]);
+    reinterpret_cast<uint4*>(dst + e * expert_bytes + frag_tile_offset(nb, kb, N / 16, KB))[frag_unit_pos(lane)] = make_uint4(words[0], words[1], words[2], words[3]);
   }
 }
 

@@ -4,14 +4,12 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "tensormap.h"
 
 namespace rb200 {
 namespace ug {
 
 template <int ZMODE, int GROUP, int SRC>
-int launch_inst(const Params& pp, int grid, size_t smem, const CUtensorMap& tw, const CUtensorMap& tx,
-                const CUtensorMap& ts, const CUtensorMap& tz, cudaStream_t stream) {
+int launch_inst(const Params& pp, int grid, size_t smem, cudaStream_t stream) {
   auto kern = umma_gemv_kernel<ZMODE, GROUP, SRC>;
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -20,16 +18,27 @@ int launch_inst(const Params& pp, int grid, size_t smem, const CUtensorMap& tw, 
     RB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured_device = dev;
   }
-  kern<<<grid, kThreads, smem, stream>>>(pp, tw, tx, ts, tz);
+  static const bool debug = getenv("RB200_DEBUG") != nullptr;
+  if (debug) {
+    int occ = -1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, smem);
+    cudaFuncAttributes fa;
+    cudaFuncGetAttributes(&fa, kern);
+    int occ0 = -1, occ64 = -1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ0, kern, kThreads, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ64, kern, kThreads, 65536);
+    fprintf(stderr, "[rb200] umma_gemv grid=%d smem=%zu stages=%d nb=%d occupancy=%d CTAs/SM (regs %d static smem %zu local %zu maxthr %d; occ@0=%d occ@64K=%d)\n", grid, smem,
+            pp.g.stages, pp.nb, occ, fa.numRegs, fa.sharedSizeBytes, fa.localSizeBytes, fa.maxThreadsPerBlock, occ0, occ64);
+  }
+  kern<<<grid, kThreads, smem, stream>>>(pp);
   RB200_CUDA(cudaGetLastError());
   return 0;
 }
 
 template <int ZMODE>
-int launch_gs(int group_code, int src, const Params& pp, int grid, size_t smem, const CUtensorMap& tw,
-              const CUtensorMap& tx, const CUtensorMap& ts, const CUtensorMap& tz, cudaStream_t stream) {
+int launch_gs(int group_code, int src, const Params& pp, int grid, size_t smem, cudaStream_t stream) {
 #define RB200_CASE(G, S) \
-  if (group_code == (G) && src == (S)) return launch_inst<ZMODE, G, S>(pp, grid, smem, tw, tx, ts, tz, stream)
+  if (group_code == (G) && src == (S)) return launch_inst<ZMODE, G, S>(pp, grid, smem, stream)
   RB200_CASE(32, kSrcGlobal);
   RB200_CASE(64, kSrcGlobal);
   RB200_CASE(128, kSrcGlobal);
@@ -80,50 +89,7 @@ int umma_gemv_run(const GemvParams& p_in, int bits, int zmode, int sm_count, flo
     else if (p.s_n == 1 && p.s_g == p.n && kChunk % p.group == 0) src = kSrcSmemKN;
   }
 
-  CUtensorMap tw, tx, ts, tz;
-  memset(&ts, 0, sizeof(ts));
-  {
-    // weight as [N/16 row blocks][K*8 bytes] in 8-byte elements; box = 8 blocks x 2 KB
-    const unsigned long long kb_total = (unsigned long long)p.k / kKBlock;
-    if (make_tensor_map_2d(&tw, p.w, CU_TENSOR_MAP_DATA_TYPE_UINT64, kb_total * 64, (unsigned long long)p.n / 16,
-                           kb_total * 512, 256, 8, CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
-      return -1;
-    // x as {64 k, m rows, K/64 blocks}: a box of 4 blocks lands as four 128B-swizzled K-major tiles
-    const unsigned long long dims[3] = {(unsigned long long)kKBlock, (unsigned long long)p.m, kb_total};
-    const unsigned long long strides[2] = {(unsigned long long)p.ldx * 2, (unsigned long long)kKBlock * 2};
-    const unsigned box[3] = {(unsigned)kKBlock, (unsigned)pp.nb, (unsigned)kBlocksPerChunk};
-    if (make_tensor_map(&tx, p.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B) != 0)
-      return -1;
-  }
-  ts = tx;
-  tz = tx;
-  if (src == kSrcSmemNK) {
-    if (make_tensor_map_2d(&ts, p.s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, kg, p.n, kg * 2, 8, kTileRows,
-                           CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
-      return -1;
-    pp.s_box_bytes = 8 * kTileRows * 2;
-    tz = ts;
-    if (zmode == kZeroGeneral && p.z) {
-      if (make_tensor_map_2d(&tz, p.z, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, kg, p.n, kg * 2, 8, kTileRows,
-                             CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
-        return -1;
-      pp.has_z_tile = 1;
-    }
-  } else if (src == kSrcSmemKN) {
-    const unsigned gpc = (unsigned)(kChunk / p.group);
-    if (make_tensor_map_2d(&ts, p.s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.n, kg, (unsigned long long)p.n * 2,
-                           kTileRows, gpc, CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
-      return -1;
-    pp.s_box_bytes = gpc * kTileRows * 2;
-    tz = ts;
-    if (zmode == kZeroGeneral && p.z) {
-      if (make_tensor_map_2d(&tz, p.z, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.n, kg,
-                             (unsigned long long)p.n * 2, kTileRows, gpc, CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
-        return -1;
-      pp.has_z_tile = 1;
-    }
-  }
+  if (src != kSrcGlobal && zmode == kZeroGeneral && p.z) pp.has_z_tile = 1;
 
   const int cpt = (p.k + kChunk - 1) / kChunk;
   const int n_tiles = p.n / kTileRows;
@@ -131,13 +97,13 @@ int umma_gemv_run(const GemvParams& p_in, int bits, int zmode, int sm_count, flo
   p.total_iters = (long long)cpt * n_tiles;
   static const int env_stages = getenv("RB200_GEMV_STAGES") ? atoi(getenv("RB200_GEMV_STAGES")) : 0;
   static const int env_grid = getenv("RB200_GEMV_GRID") ? atoi(getenv("RB200_GEMV_GRID")) : 0;
-  long long grid = (long long)sm_count * 2;  // two persistent CTAs per SM, half the tensor memory each
+  long long grid = (long long)sm_count;  // one persistent CTA per SM (tensor-memory kernels get occupancy 1)
   if (env_grid > 0) grid = env_grid;
   if (grid > p.total_iters) grid = p.total_iters;
 
   const Layout lay = make_layout(pp.nb, src, zmode);
   const size_t fixed = 1024 /* alignment slack */ + (size_t)(2 * 16 + 2 * kNumA + 2 * kNumD) * sizeof(uint64_t) + 16;
-  const size_t budget = (size_t)(228 * 1024) / 2 - 1024 - 512;
+  const size_t budget = (size_t)227 * 1024;
   int stages = (int)((budget - fixed) / lay.stage_bytes);
   if (env_stages > 0) stages = env_stages;
   if (stages > 16) stages = 16;
@@ -153,8 +119,8 @@ int umma_gemv_run(const GemvParams& p_in, int bits, int zmode, int sm_count, flo
   pp.epoch = epoch;
 
   if (zmode == kZeroConstInt)
-    return launch_gs<kZeroConstInt>(group_code, src, pp, (int)grid, smem, tw, tx, ts, tz, stream);
-  return launch_gs<kZeroGeneral>(group_code, src, pp, (int)grid, smem, tw, tx, ts, tz, stream);
+    return launch_gs<kZeroConstInt>(group_code, src, pp, (int)grid, smem, stream);
+  return launch_gs<kZeroGeneral>(group_code, src, pp, (int)grid, smem, stream);
 }
 
 }  // namespace rb200

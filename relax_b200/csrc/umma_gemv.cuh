@@ -6,21 +6,23 @@
 // dequantised weights are the A operand of tcgen05.mma and live in tensor memory; the batch is
 // the MMA's N (16 or 32), so one instruction covers 128 weight rows x 16 k for the whole batch.
 //
-//   producer warp  : three TMA tile loads per (128-row tile, 256-k chunk) into a ring of
-//                    shared-memory stages - the 16 KB packed-weight slice (8 row blocks x 2 KB,
-//                    one 2-D box over the fragment-ordered weight), the x slice (128B-swizzled
-//                    K-major, one 3-D box) and the scale tile.  Few large loads per stage:
-//                    issuing a dozen small copies per stage capped the pipeline at ~3 TB/s
-//   8 decode warps : two groups of four warps; group i takes the blocks 2h + i of every chunk
-//                    (h = 0, 1).  thread = one weight row = one TMEM lane; reads its row's packed
+//   producer warp  : one bulk async copy per (128-row tile, 256-k chunk): the fragment layout
+//                    keeps that 16 KB slice contiguous (the copy engine pays per contiguous
+//                    segment; measured: 8 x 2 KB segments per stage halve an SM's streaming rate)
+//   loader warp    : x slice and scale / zero tiles with 16-byte cp.async straight into the
+//                    layouts their readers want (x: 128B-swizzled K-major tensor-core operand),
+//                    completion counted on the stage's mbarrier (cp.async.mbarrier.arrive)
+//   16 decode warps: four groups of four warps; group i takes the i-th 64-k block of every
+//                    chunk.  thread = one weight row = one TMEM lane; reads its row's packed
 //                    nibbles from the fragment-ordered stage, decodes them bit-exactly (lop3 +
 //                    exact .rn fp16 ops), writes 64 k of fp16 into its quarter of a TMEM A buffer
 //                    with tcgen05.st
-//   MMA warp       : one thread waits once per half chunk and issues 8 x tcgen05.mma (M=128,
+//   MMA warp       : one thread waits once per chunk and issues 16 x tcgen05.mma (M=128,
 //                    N=16|32, K=16), A from TMEM, B = x tile from shared memory, fp32
-//                    accumulators in TMEM; tcgen05.commit recycles A buffers and stages
-//                    (hand-offs per 128 k, not per 64-k block, to keep the single issuing
-//                    thread off the critical path)
+//                    accumulators in TMEM; tcgen05.commit recycles A buffers and stages.
+//                    A kernel that allocates tensor memory runs one CTA per SM (the occupancy
+//                    calculator reports 1 whatever its other resources), so the CTA is sized to
+//                    fill the SM: 19 warps, all 512 TMEM columns, ~220 KB of stages.
 //   epilogue       : the decode warps read the accumulator with tcgen05.ld, apply bias /
 //                    activation / residual, round once to fp16 and store.
 //
@@ -44,8 +46,9 @@
 namespace rb200 {
 namespace ug {
 
-constexpr int kDecodeWarps = 8;                 // two groups of four (one group = 128 TMEM lanes)
-constexpr int kThreads = (2 + kDecodeWarps) * 32;
+constexpr int kDecodeWarps = 16;                // four groups of four (one group = 128 TMEM lanes)
+constexpr int kFirstDecodeWarp = 4;             // warps 0..2: producer, MMA, loader; 3 idle; 4.. decode
+constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;
 constexpr int kTileRows = 128;
 constexpr int kKBlock = 64;                     // k per MMA block (4 x K=16) and per fragment tile
 constexpr int kBlocksPerChunk = 4;              // 256 k per stage
@@ -53,11 +56,10 @@ constexpr int kChunk = kKBlock * kBlocksPerChunk;
 constexpr int kWBlockPitch = 2048;              // 16-row block slice of a stage (4 fragment tiles)
 constexpr int kWBytes = 8 * kWBlockPitch;
 constexpr int kScaleBoxBytes = 2048;
-constexpr int kNumA = 2;                        // TMEM A buffers, half a chunk (two 64-k blocks, 64 columns) each
-constexpr int kACols = 64;
+constexpr int kNumA = 3;                        // TMEM A buffers, one whole 256-k chunk each (128 columns)
+constexpr int kACols = 32 * kBlocksPerChunk;
 constexpr int kNumD = 3;                        // accumulators: two for whole tiles, one for the owned piece
-constexpr int kTmemCols = 256;                  // half the tensor memory: two CTAs per SM (one CTA alone
-                                                // cannot pull more than ~4.4 TB/s through its copy pipeline)
+constexpr int kTmemCols = 512;                  // the whole tensor memory (one CTA per SM)
 
 enum ScaleSrc : int { kSrcGlobal = 0, kSrcSmemNK = 1, kSrcSmemKN = 2 };
 
@@ -89,21 +91,14 @@ inline Layout make_layout(int nb, int src, int zmode) {
 #ifdef __CUDACC__
 
 // ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-      : "memory");
+// 16-byte asynchronous copy global -> shared; bytes beyond src_bytes are written as zero
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes)
+               : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
-      : "memory");
+// the mbarrier gets one (pre-counted) arrival once all earlier cp.async of this thread have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)),
@@ -327,10 +322,8 @@ __device__ __forceinline__ void decode_block_kb(int kb, const GemvParams& p, con
 }
 
 template <int ZMODE, int GROUP, int SRC>
-__global__ void __launch_bounds__(kThreads, 2)
-    umma_gemv_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_w,
-                     const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_s,
-                     const __grid_constant__ CUtensorMap tmap_z) {
+__global__ void __launch_bounds__(kThreads, 1)
+    umma_gemv_kernel(const Params pp) {
   extern __shared__ uint8_t smem_raw[];
   const GemvParams& p = pp.g;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -358,8 +351,8 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&stage_full[s], 1);
-      mbar_init(&stage_empty[s], kDecodeWarps + 1);
+      mbar_init(&stage_full[s], 1 + 32);            // producer's expect_tx arrival + 32 loader lanes
+      mbar_init(&stage_empty[s], kDecodeWarps + 1);  // decode warps + the MMA thread's commit
     }
     for (int i = 0; i < kNumA; ++i) {
       mbar_init(&a_full[i], kDecodeWarps);
@@ -382,6 +375,14 @@ __global__ void __launch_bounds__(kThreads, 2)
   const uint32_t a_col0 = tmem_base;                  // kNumA buffers of kACols columns
   const uint32_t d_col0 = tmem_base + kNumA * kACols; // kNumD accumulators of up to 32 columns
 
+  // x rows >= m of every stage are never written by the loader: they must read as zero
+  for (int st = 0; st < stages; ++st) {
+    uint4* xs = reinterpret_cast<uint4*>(smem + (size_t)st * stage_bytes);
+    for (int i = tid; i < x_bytes / 16; i += kThreads) xs[i] = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async();
+  __syncthreads();
+
   const long long total = p.total_iters;
   const long long grid = gridDim.x;
 #ifdef RB200_ABLATE
@@ -396,58 +397,84 @@ __global__ void __launch_bounds__(kThreads, 2)
   bool ok = true;
 
   if (warp == 0) {
-    // ============================================================ producer
+    // ============================================================ producer: packed weights
     int stage = 0;
     uint32_t phase = 0;
     Piece pc;
     for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
-      const int blk0 = pc.tile * 8;
       for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
-        if ((ablate & 2048) ? !mbar_wait_bounded(&stage_empty[stage], phase ^ 1u, p.status)
-                            : !mbar_wait_relaxed(&stage_empty[stage], phase ^ 1u, p.status)) {
+        if (!mbar_wait_relaxed(&stage_empty[stage], phase ^ 1u, p.status)) {
           ok = false;
           break;
         }
-        const int kb0 = chunk * kBlocksPerChunk;
-        const int nkb = min(kBlocksPerChunk, kb_total - kb0);
-        uint8_t* sbase = smem + (size_t)stage * stage_bytes;
-        // every load delivers its full box (out-of-range parts arrive as zeros)
-        uint32_t tx = (uint32_t)kWBytes;
-        if (!(ablate & 16)) tx += (uint32_t)kBlocksPerChunk * nb * 128;
-        if (SRC != kSrcGlobal && !(ablate & 32)) tx += pp.s_box_bytes * (pp.has_z_tile ? 2u : 1u);
-        if (lane == 0) mbar_arrive_expect_tx(&stage_full[stage], tx);
+        if (lane == 0) {
+          const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
+          const uint32_t wbytes = (uint32_t)nkb * 8 * 512;  // 8 row blocks x nkb fragment tiles, contiguous
+          mbar_arrive_expect_tx(&stage_full[stage], wbytes);
+          bulk_g2s(smem + (size_t)stage * stage_bytes + w_off,
+                   p.w + frag_stage_offset(pc.tile, chunk, p.n / 16, kb_total), wbytes, &stage_full[stage]);
+        }
         __syncwarp();
-        (void)nkb;
-        if (ablate & 128) {
-          if (lane >= 16 && lane < 24) {
-            const int b = lane - 16;
-            const uint8_t* src = p.w + ((size_t)(blk0 + b) * kb_total + kb0) * 512;
-            bulk_g2s(sbase + w_off + b * kWBlockPitch, src, 2048, &stage_full[stage]);
-          }
-        }
-        if (lane == 0 && !(ablate & 128)) {
-          // weight: rows = 16-row blocks, inner = that block's bytes in 8-byte elements
-          tma_load_2d(sbase + w_off, &tmap_w, kb0 * 64, blk0, &stage_full[stage]);
-        } else if (lane == 1 && !(ablate & 16)) {
-          // x: {k inside a 64-block, batch row, 64-block} -> four [nb rows][64 k] sub-tiles, 128B swizzle
-          tma_load_3d(sbase, &tmap_x, 0, 0, kb0, &stage_full[stage]);
-        } else if (SRC != kSrcGlobal && lane == 12 && !(ablate & 32)) {
-          constexpr int kGroupsPerChunk = GROUP > 0 ? (kChunk / GROUP) : 1;
-          const int gc0 = chunk * kGroupsPerChunk;
-          if (SRC == kSrcSmemNK) tma_load_2d(sbase + s_off, &tmap_s, gc0, blk0 * 16, &stage_full[stage]);
-          else tma_load_2d(sbase + s_off, &tmap_s, blk0 * 16, gc0, &stage_full[stage]);
-        } else if (SRC != kSrcGlobal && ZMODE == kZeroGeneral && lane == 13 && pp.has_z_tile) {
-          constexpr int kGroupsPerChunk = GROUP > 0 ? (kChunk / GROUP) : 1;
-          const int gc0 = chunk * kGroupsPerChunk;
-          if (SRC == kSrcSmemNK) tma_load_2d(sbase + z_off, &tmap_z, gc0, blk0 * 16, &stage_full[stage]);
-          else tma_load_2d(sbase + z_off, &tmap_z, blk0 * 16, gc0, &stage_full[stage]);
-        }
         if (++stage == stages) {
           stage = 0;
           phase ^= 1u;
         }
       }
     }
+  } else if (warp == 2) {
+    // ============================================================ loader: x, scales, zero points
+    int stage = 0;
+    uint32_t phase = 0;
+    Piece pc;
+    const int j = lane >> 3, c16 = lane & 7;  // x: 64-k sub-tile and 16-byte chunk handled by this lane
+    const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
+    for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
+      const int64_t n0 = (int64_t)pc.tile * kTileRows;
+      for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
+        if (!mbar_wait_relaxed(&stage_empty[stage], phase ^ 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        uint8_t* sbase = smem + (size_t)stage * stage_bytes;
+        // x[r, chunk*256 + lane*8 .. +8) -> sub-tile j, row r, 16-byte chunk c16 ^ (r & 7)
+        const int64_t kcol = (int64_t)chunk * kChunk + lane * 8;
+        const uint32_t xvalid = kcol < p.k ? 16u : 0u;
+        const __half* xsrc = p.x + (xvalid ? kcol : 0);
+        for (int r = 0; r < p.m; ++r)
+          cp_async16(sbase + j * nb * 128 + r * 128 + ((c16 ^ (r & 7)) << 4), xsrc + (int64_t)r * p.ldx, xvalid);
+        if (SRC == kSrcSmemNK) {
+          // [128 rows][8 groups]: 16 bytes per row, four rows per lane
+          const int64_t g0 = (int64_t)chunk * 8;
+          const int64_t left = (kg - g0) * 2;
+          const uint32_t sv = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int row = lane + 32 * i;
+            const int64_t o = (n0 + row) * kg + (sv ? g0 : 0);
+            cp_async16(sbase + s_off + row * 16, p.s + o, sv);
+            if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + z_off + row * 16, p.z + o, sv);
+          }
+        } else if (SRC == kSrcSmemKN) {
+          // [groups of the chunk][128 rows]: 256 bytes per group row
+          constexpr int kG = GROUP > 0 ? (kChunk / GROUP) : 1;
+          for (int i = lane; i < kG * 16; i += 32) {
+            const int gl = i >> 4, cc = i & 15;
+            const int64_t grow = (int64_t)chunk * kG + gl;
+            const uint32_t sv = grow < kg ? 16u : 0u;
+            const int64_t o = (sv ? grow : 0) * p.n + n0 + cc * 8;
+            cp_async16(sbase + s_off + gl * 256 + cc * 16, p.s + o, sv);
+            if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + z_off + gl * 256 + cc * 16, p.z + o, sv);
+          }
+        }
+        cp_async_arrive(&stage_full[stage]);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    // drain this thread's copies before the block can retire
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else if (warp == 1) {
     // ============================================================ MMA issuer (one thread)
     if (lane == 0) {
@@ -467,44 +494,32 @@ __global__ void __launch_bounds__(kThreads, 2)
         tc_fence_after();
         const uint32_t d_tmem = d_col0 + db * 32;
         bool first = true;
-        for (int chunk = pc.c0; ok && chunk < pc.c1; ++chunk) {
-          if (!((ablate & 4096) ? mbar_wait_bounded(&stage_full[stage], phase, p.status) : mbar_wait_relaxed(&stage_full[stage], phase, p.status))) {
+        for (int chunk = pc.c0; ok && chunk < pc.c1; ++chunk, ++q) {
+          if (!mbar_wait_relaxed(&stage_full[stage], phase, p.status)) {
             ok = false;
             break;
           }
-          const int kb0 = chunk * kBlocksPerChunk;
-          const int nkb = min(kBlocksPerChunk, kb_total - kb0);
+          // x was written by cp.async (generic proxy): order it before the tensor core's reads
+          fence_proxy_async();
+          const uint32_t ab = q % kNumA;
+          if (!mbar_wait_relaxed(&a_full[ab], (q / kNumA) & 1u, p.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
           const uint32_t xbase = smem_u32(smem + (size_t)stage * stage_bytes);
-          for (int h = 0; h < 2; ++h, ++q) {
-            const uint32_t ab = q % kNumA;
-            if (!(ablate & 256) && !((ablate & 4096) ? mbar_wait_bounded(&a_full[ab], (q / kNumA) & 1u, p.status) : mbar_wait_relaxed(&a_full[ab], (q / kNumA) & 1u, p.status))) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            for (int kb = 2 * h; kb < min(nkb, 2 * h + 2); ++kb) {
-              const uint32_t a_tmem = a_col0 + ab * kACols + (kb & 1) * 32;
+          for (int kb = 0; kb < nkb; ++kb) {
+            const uint32_t a_tmem = a_col0 + ab * kACols + kb * 32;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if ((ablate & 4) && !(first && j == 0)) continue;
-                const uint64_t bdesc = make_b_desc(xbase + kb * nb * 128 + j * 32);
-                tc_mma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
-              }
-              first = false;
+            for (int j = 0; j < 4; ++j) {
+              if ((ablate & 4) && !(first && j == 0)) continue;
+              const uint64_t bdesc = make_b_desc(xbase + kb * nb * 128 + j * 32);
+              tc_mma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
             }
-            if (ablate & 256) {
-            } else if (ablate & 64) mbar_arrive(&a_empty[ab]);
-            else tc_commit(&a_empty[ab]);
+            first = false;
           }
-          if (!ok) break;
-          if (ablate & 64) {
-            if (!(ablate & 512)) mbar_arrive(&stage_empty[stage]);
-            if (++stage == stages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-            continue;
-          }
+          tc_commit(&a_empty[ab]);
           tc_commit(&stage_empty[stage]);
           if (++stage == stages) {
             stage = 0;
@@ -514,10 +529,10 @@ __global__ void __launch_bounds__(kThreads, 2)
         tc_commit(&d_full[db]);
       }
     }
-  } else {
+  } else if (warp >= kFirstDecodeWarp) {
     // ============================================================ decode + epilogue warps
-    const int dw = warp - 2;
-    const int grp = dw >> 2;             // which 64-k block of every chunk this warp decodes
+    const int dw = warp - kFirstDecodeWarp;
+    const int grp = dw >> 2;             // which 64-k block of every chunk this warp decodes (0..3)
     const int w4 = warp & 3;             // TMEM lane quadrant of this warp
     const int hi = w4 & 1;               // rows g (0) or g+8 (1) of the 16-row blocks
     const int bl = (w4 >> 1) * 4 + (lane >> 3);  // 16-row block inside the tile
@@ -556,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         const int nkb = min(kBlocksPerChunk, kb_total - kb0);
         const uint8_t* sbase = smem + (size_t)stage * stage_bytes;
         RowCtx c;
-        c.wblk = sbase + w_off + bl * kWBlockPitch;
+        c.wblk = sbase + w_off + bl * (nkb * 512);
 #pragma unroll
         for (int t = 0; t < 4; ++t) c.unit_off[t] = unit_off[t];
         c.s_tile = sbase + s_off;
@@ -572,37 +587,36 @@ __global__ void __launch_bounds__(kThreads, 2)
         c.row = row;
         c.n_row = n_row;
         c.kb0 = kb0;
-        for (int h = 0; h < 2 && ok; ++h, ++q) {
-          const uint32_t ab = q % kNumA;
-          if (!(ablate & 256) && !mbar_wait_bounded(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const int kb = 2 * h + grp;
-          if (kb < nkb) {
-            uint32_t regs[32];
-            if (ablate & 1) {
-#pragma unroll
-              for (int t = 0; t < 32; ++t) regs[t] = 0x3c003c00u;
-            } else if (hi) {
-              decode_block_kb<ZMODE, GROUP, SRC, 1>(kb, p, pp, c, zc, zconst_h2, group, regs);
-            } else {
-              decode_block_kb<ZMODE, GROUP, SRC, 0>(kb, p, pp, c, zc, zconst_h2, group, regs);
-            }
-            if (!(ablate & 2)) {
-              tc_st32(lane_taddr | (a_col0 + ab * kACols + grp * 32), regs);
-              tc_wait_st();
-            }
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0 && !(ablate & 256)) mbar_arrive(&a_full[ab]);
+        const int nkb_c = nkb;
+        const uint32_t ab = q % kNumA;
+        if (!mbar_wait_bounded(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
+          ok = false;
+          break;
         }
-        if (!ok) break;
+        ++q;
+        tc_fence_after();
+        const int kb = grp;
+        if (kb < nkb_c) {
+          uint32_t regs[32];
+          if (ablate & 1) {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) regs[t] = 0x3c003c00u;
+          } else if (hi) {
+            decode_block_kb<ZMODE, GROUP, SRC, 1>(kb, p, pp, c, zc, zconst_h2, group, regs);
+          } else {
+            decode_block_kb<ZMODE, GROUP, SRC, 0>(kb, p, pp, c, zc, zconst_h2, group, regs);
+          }
+          if (!(ablate & 2)) {
+            tc_st32(lane_taddr | (a_col0 + ab * kACols + kb * 32), regs);
+            tc_wait_st();
+          }
+        }
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&stage_empty[stage]);
-        if ((ablate & 512) && warp == 2 && lane == 0) mbar_arrive(&stage_empty[stage]);
+        if (lane == 0) {
+          mbar_arrive(&a_full[ab]);
+          mbar_arrive(&stage_empty[stage]);
+        }
         if (++stage == stages) {
           stage = 0;
           phase ^= 1u;
@@ -617,8 +631,8 @@ __global__ void __launch_bounds__(kThreads, 2)
         ++d_uses[db];
         continue;
       }
-      // one group drains a given accumulator: whole tiles alternate, tail pieces group 0
-      const int drain_grp = (pc.kind == kWhole) ? (db & 1) : 0;
+      // one group drains a given accumulator: whole tiles groups 0 / 1, tail pieces group 2
+      const int drain_grp = (pc.kind == kWhole) ? (db & 1) : 2;
       const uint32_t use = d_uses[db]++;
       if (grp != drain_grp) continue;
       if (!mbar_wait_bounded(&d_full[db], use & 1u, p.status)) {
@@ -655,7 +669,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
 
     // ------------------------------------------------------------ fix-up of the owned tile
-    if (ok && have_head && grp == 1) {
+    if (ok && have_head && grp == 3) {
       const int db = 2;
       if (mbar_wait_bounded(&d_full[db], 0u, p.status)) {
         tc_fence_after();

@@ -18,6 +18,29 @@ def _place_units(tiles: np.ndarray) -> np.ndarray:
     return out
 
 
+def tile_offset(nb: int, kb: int, NB: int, KB: int) -> int:
+    """Byte offset of fragment tile (nb, kb): tiles of one (128-row tile, 4-k-block chunk) are contiguous."""
+    t, b, c, j = nb // 8, nb % 8, kb // 4, kb % 4
+    nblk = min(8, NB - 8 * t)
+    nkb = min(4, KB - 4 * c)
+    return ((t * 8 * KB) + c * 4 * nblk + b * nkb + j) * 512
+
+
+def _order_tiles(tiles: np.ndarray) -> np.ndarray:
+    """tiles uint8 [NB, KB, 512] -> flat bytes in storage order."""
+    NB, KB, _ = tiles.shape
+    out = np.empty(NB * KB * 512, dtype=np.uint8)
+    seen = np.zeros(NB * KB, dtype=bool)
+    for nb in range(NB):
+        for kb in range(KB):
+            o = tile_offset(nb, kb, NB, KB)
+            assert o % 512 == 0 and not seen[o // 512]
+            seen[o // 512] = True
+            out[o:o + 512] = tiles[nb, kb]
+    assert seen.all()
+    return out
+
+
 def fragment_layout(codes: np.ndarray, bits: int) -> np.ndarray:
     """codes uint8 [N, K] (unsigned) -> uint8 flat array of N*K*bits/8 bytes."""
     n, k = codes.shape
@@ -33,10 +56,10 @@ def fragment_layout(codes: np.ndarray, bits: int) -> np.ndarray:
                 words |= c[:, r2, :, :, :, :, cc] << np.uint32(4 * slot[r2, cc])
         # memory order: nb, kb, unit position of lane (g, t), j
         tiles = words.transpose(0, 2, 1, 3, 4).reshape(n // 16, kb, 32, 4)  # [nb, kb, lane=4g+t, j]
-        return _place_units(tiles).reshape(-1).astype("<u4").view(np.uint8)
+        return _order_tiles(_place_units(tiles).astype("<u4").view(np.uint8).reshape(n // 16, kb, 512))
     kb = k // 32
     # [nb, r2, g, kb, t, j, c] with k = kb*32 + t*8 + j*4 + c
     c = codes.reshape(n // 16, 2, 8, kb, 4, 2, 4)
     # memory order: nb, kb, unit position of lane (g, t), then (j, r2, c) inside the 16-byte unit
     tiles = np.ascontiguousarray(c.transpose(0, 3, 2, 4, 5, 1, 6)).reshape(n // 16, kb, 32, 16)
-    return _place_units(tiles).reshape(-1).astype(np.uint8)
+    return _order_tiles(_place_units(tiles).astype(np.uint8).reshape(n // 16, kb, 512))
