@@ -216,6 +216,17 @@ int rb200_check_async_error(void* stream, int* status_out) {
   return 0;
 }
 
+#ifdef RB200_ABLATE
+// instrumented builds only: copy a range of the library's partial-sum scratch to the host
+RB200_API int rb200_debug_read_scratch(void* dst, size_t offset_bytes, size_t bytes) {
+  DeviceScratch* sc = device_scratch(0, 0);
+  if (!sc) return -1;
+  RB200_CUDA(cudaDeviceSynchronize());
+  RB200_CUDA(cudaMemcpy(dst, reinterpret_cast<uint8_t*>(sc->partials) + offset_bytes, bytes, cudaMemcpyDeviceToHost));
+  return 0;
+}
+#endif
+
 int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int64_t k, int64_t n,
                             int is_int4, int src_layout, void* stream) {
   RB200_CHECK(src && dst, "src and dst must be non-NULL");

@@ -101,6 +101,28 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or
+// the hint (ns) expires, so a waiting warp neither burns issue slots nor wakes late.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, int* status) {
+  // each try parks the thread for up to ~10 us; 200k tries bound the wait to about two seconds
+#pragma unroll 1
+  for (int i = 0; i < 200000; ++i)
+    if (mbar_try_wait_hint(bar, parity, 10000u)) return true;
+  if (status) atomicExch(status, kStatusWaitTimeout);
+  return false;
+}
+
 // Same, for roles with slack (producer, MMA issuer): sleeps between polls so the waiting warp
 // does not take issue slots from the warps doing the arithmetic.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int* status) {

@@ -12,8 +12,10 @@
 //   loader warp    : x slice and scale / zero tiles with 16-byte cp.async straight into the
 //                    layouts their readers want (x: 128B-swizzled K-major tensor-core operand),
 //                    completion counted on the stage's mbarrier (cp.async.mbarrier.arrive)
-//   16 decode warps: four groups of four warps; group i takes the i-th 64-k block of every
-//                    chunk.  thread = one weight row = one TMEM lane; reads its row's packed
+//   8 decode warps : two groups of four warps; group i takes the 64-k blocks i and i + 2 of
+//                    every chunk (two blocks per hand-off keep the per-stage bookkeeping small
+//                    against the decode arithmetic - the kernel is instruction-issue bound).
+//                    thread = one weight row = one TMEM lane; reads its row's packed
 //                    nibbles from the fragment-ordered stage, decodes them bit-exactly (lop3 +
 //                    exact .rn fp16 ops), writes 64 k of fp16 into its quarter of a TMEM A buffer
 //                    with tcgen05.st
@@ -22,7 +24,7 @@
 //                    accumulators in TMEM; tcgen05.commit recycles A buffers and stages.
 //                    A kernel that allocates tensor memory runs one CTA per SM (the occupancy
 //                    calculator reports 1 whatever its other resources), so the CTA is sized to
-//                    fill the SM: 19 warps, all 512 TMEM columns, ~220 KB of stages.
+//                    fill the SM: all 512 TMEM columns, ~220 KB of stages.
 //   epilogue       : the decode warps read the accumulator with tcgen05.ld, apply bias /
 //                    activation / residual, round once to fp16 and store.
 //
@@ -46,7 +48,7 @@
 namespace rb200 {
 namespace ug {
 
-constexpr int kDecodeWarps = 16;                // four groups of four (one group = 128 TMEM lanes)
+constexpr int kDecodeWarps = 8;                 // two groups of four (one group = 128 TMEM lanes)
 constexpr int kFirstDecodeWarp = 4;             // warps 0..2: producer, MMA, loader; 3 idle; 4.. decode
 constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;
 constexpr int kTileRows = 128;
@@ -387,7 +389,17 @@ __global__ void __launch_bounds__(kThreads, 1)
   const long long grid = gridDim.x;
 #ifdef RB200_ABLATE
   const int ablate = p.ablate;
+  unsigned long long* tl = (blockIdx.x == 0 && (ablate & 65536)) ? reinterpret_cast<unsigned long long*>(pp.partial) + (1 << 18) : nullptr;
+#define RB200_TL(role, i)                                                          \
+  do {                                                                             \
+    if (tl && (i) < 256) {                                                         \
+      unsigned long long t_;                                                       \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                        \
+      tl[(role) * 256 + (i)] = t_;                                                 \
+    }                                                                              \
+  } while (0)
 #else
+#define RB200_TL(role, i) do {} while (0)
   constexpr int ablate = 0;
 #endif
   const long long it0 = range_start(blockIdx.x, total, grid);
@@ -398,16 +410,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == 0) {
     // ============================================================ producer: packed weights
+    int tl_i = 0;
+    (void)tl_i;
     int stage = 0;
     uint32_t phase = 0;
     Piece pc;
     for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
       for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
-        if (!mbar_wait_relaxed(&stage_empty[stage], phase ^ 1u, p.status)) {
+        if (!mbar_wait_parked(&stage_empty[stage], phase ^ 1u, p.status)) {
           ok = false;
           break;
         }
         if (lane == 0) {
+          RB200_TL(0, tl_i); ++tl_i;
           const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
           const uint32_t wbytes = (uint32_t)nkb * 8 * 512;  // 8 row blocks x nkb fragment tiles, contiguous
           mbar_arrive_expect_tx(&stage_full[stage], wbytes);
@@ -431,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
       const int64_t n0 = (int64_t)pc.tile * kTileRows;
       for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
-        if (!mbar_wait_relaxed(&stage_empty[stage], phase ^ 1u, p.status)) {
+        if (!mbar_wait_parked(&stage_empty[stage], phase ^ 1u, p.status)) {
           ok = false;
           break;
         }
@@ -440,9 +455,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int64_t kcol = (int64_t)chunk * kChunk + lane * 8;
         const uint32_t xvalid = kcol < p.k ? 16u : 0u;
         const __half* xsrc = p.x + (xvalid ? kcol : 0);
+        if (!(ablate & 16))
         for (int r = 0; r < p.m; ++r)
           cp_async16(sbase + j * nb * 128 + r * 128 + ((c16 ^ (r & 7)) << 4), xsrc + (int64_t)r * p.ldx, xvalid);
-        if (SRC == kSrcSmemNK) {
+        if (ablate & 32) {
+        } else if (SRC == kSrcSmemNK) {
           // [128 rows][8 groups]: 16 bytes per row, four rows per lane
           const int64_t g0 = (int64_t)chunk * 8;
           const int64_t left = (kg - g0) * 2;
@@ -486,7 +503,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       Piece pc;
       for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, &pc); ++idx) {
         const int db = pc.dbuf;
-        if (!mbar_wait_relaxed(&d_empty[db], (d_uses[db] & 1u) ^ 1u, p.status)) {
+        if (!mbar_wait_parked(&d_empty[db], (d_uses[db] & 1u) ^ 1u, p.status)) {
           ok = false;
           break;
         }
@@ -495,18 +512,28 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t d_tmem = d_col0 + db * 32;
         bool first = true;
         for (int chunk = pc.c0; ok && chunk < pc.c1; ++chunk, ++q) {
-          if (!mbar_wait_relaxed(&stage_full[stage], phase, p.status)) {
+          if (!mbar_wait_parked(&stage_full[stage], phase, p.status)) {
             ok = false;
             break;
           }
+          if (ablate & 32768) {
+            mbar_arrive(&stage_empty[stage]);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
+          RB200_TL(4, (int)q);
           // x was written by cp.async (generic proxy): order it before the tensor core's reads
           fence_proxy_async();
           const uint32_t ab = q % kNumA;
-          if (!mbar_wait_relaxed(&a_full[ab], (q / kNumA) & 1u, p.status)) {
+          if (!(ablate & 256) && !mbar_wait_parked(&a_full[ab], (q / kNumA) & 1u, p.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          RB200_TL(5, (int)q);
           const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
           const uint32_t xbase = smem_u32(smem + (size_t)stage * stage_bytes);
           for (int kb = 0; kb < nkb; ++kb) {
@@ -519,8 +546,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             first = false;
           }
-          tc_commit(&a_empty[ab]);
-          tc_commit(&stage_empty[stage]);
+          if (ablate & 64) {
+            mbar_arrive(&a_empty[ab]);
+            mbar_arrive(&stage_empty[stage]);
+          } else {
+            tc_commit(&a_empty[ab]);
+            tc_commit(&stage_empty[stage]);
+          }
+          RB200_TL(6, (int)q);
           if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
@@ -532,7 +565,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp >= kFirstDecodeWarp) {
     // ============================================================ decode + epilogue warps
     const int dw = warp - kFirstDecodeWarp;
-    const int grp = dw >> 2;             // which 64-k block of every chunk this warp decodes (0..3)
+    const int grp = dw >> 2;             // this warp decodes the 64-k blocks grp and grp + 2 of every chunk
     const int w4 = warp & 3;             // TMEM lane quadrant of this warp
     const int hi = w4 & 1;               // rows g (0) or g+8 (1) of the 16-row blocks
     const int bl = (w4 >> 1) * 4 + (lane >> 3);  // 16-row block inside the tile
@@ -563,10 +596,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row * p.s_n]);
       }
       for (int chunk = pc.c0; ok && chunk < pc.c1; ++chunk) {
-        if (!mbar_wait_bounded(&stage_full[stage], phase, p.status)) {
+        if (!mbar_wait_parked(&stage_full[stage], phase, p.status)) {
           ok = false;
           break;
         }
+        if (ablate & 16384) {
+          ++q;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&stage_empty[stage]);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          continue;
+        }
+        if (warp == kFirstDecodeWarp && lane == 0) RB200_TL(1, (int)q);
         const int kb0 = chunk * kBlocksPerChunk;
         const int nkb = min(kBlocksPerChunk, kb_total - kb0);
         const uint8_t* sbase = smem + (size_t)stage * stage_bytes;
@@ -589,14 +633,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         c.kb0 = kb0;
         const int nkb_c = nkb;
         const uint32_t ab = q % kNumA;
-        if (!mbar_wait_bounded(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
+        if (!(ablate & 256) && !mbar_wait_parked(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
           ok = false;
           break;
         }
+        if (warp == kFirstDecodeWarp && lane == 0) RB200_TL(2, (int)q);
         ++q;
         tc_fence_after();
-        const int kb = grp;
-        if (kb < nkb_c) {
+#pragma unroll 1
+        for (int kb = grp; kb < nkb_c; kb += 2) {
           uint32_t regs[32];
           if (ablate & 1) {
 #pragma unroll
@@ -606,15 +651,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           } else {
             decode_block_kb<ZMODE, GROUP, SRC, 0>(kb, p, pp, c, zc, zconst_h2, group, regs);
           }
-          if (!(ablate & 2)) {
-            tc_st32(lane_taddr | (a_col0 + ab * kACols + kb * 32), regs);
-            tc_wait_st();
-          }
+          if (!(ablate & 2)) tc_st32(lane_taddr | (a_col0 + ab * kACols + kb * 32), regs);
         }
+        if (!(ablate & 2)) tc_wait_st();
         tc_fence_before();
         __syncwarp();
+        if (warp == kFirstDecodeWarp && lane == 0) RB200_TL(3, (int)q - 1);
         if (lane == 0) {
-          mbar_arrive(&a_full[ab]);
+          if (!(ablate & 256)) mbar_arrive(&a_full[ab]);
           mbar_arrive(&stage_empty[stage]);
         }
         if (++stage == stages) {
@@ -631,11 +675,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         ++d_uses[db];
         continue;
       }
-      // one group drains a given accumulator: whole tiles groups 0 / 1, tail pieces group 2
-      const int drain_grp = (pc.kind == kWhole) ? (db & 1) : 2;
+      // one group drains a given accumulator: whole tiles alternate, tail pieces group 0
+      const int drain_grp = (pc.kind == kWhole) ? (db & 1) : 0;
       const uint32_t use = d_uses[db]++;
       if (grp != drain_grp) continue;
-      if (!mbar_wait_bounded(&d_full[db], use & 1u, p.status)) {
+      if (!mbar_wait_parked(&d_full[db], use & 1u, p.status)) {
         ok = false;
         break;
       }
@@ -669,9 +713,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ------------------------------------------------------------ fix-up of the owned tile
-    if (ok && have_head && grp == 3) {
+    if (ok && have_head && grp == 1) {
       const int db = 2;
-      if (mbar_wait_bounded(&d_full[db], 0u, p.status)) {
+      if (mbar_wait_parked(&d_full[db], 0u, p.status)) {
         tc_fence_after();
         // contributors: the CTAs after this one whose range reaches into head_tile
         const long long hi_it = (long long)head_tile * cpt + cpt - 1;

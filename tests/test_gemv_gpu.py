@@ -241,3 +241,32 @@ def test_m_zero_and_bad_shapes_rejected(oracle):
         ops.gemm_fp16_q4f16(torch.zeros(1, 128, dtype=torch.float16, device="cuda"), pre, to_dev(case.scales))
     with pytest.raises(relax_b200.RB200Error):
         ops.preprocess_weight_q4f16(torch.zeros(24, 8, dtype=torch.int32, device="cuda"))  # n % 16 != 0
+
+
+@pytest.mark.parametrize("m,k,n,group,asym", [(33, 512, 256, 32, False), (100, 1024, 384, 128, True), (256, 512, 128, 32, False)])
+def test_large_batch_q4(oracle, m, k, n, group, asym):
+    """m > 32 (sliced over the batch): same parity bar as the decode path."""
+    case = synth.q4_case(np.random.Generator(np.random.PCG64(m + k)), m, k, n, group, asymmetric=asym)
+    rs = np.random.RandomState(m)
+    bias = rs.randn(m, n).astype(np.float16)
+    res = rs.randn(m, n).astype(np.float16)
+    got, exp = _run_q4(oracle, case, bias=bias, residual=res, binary_op="plus", activation="relu")
+    assert_close(got, exp, tight=False)
+
+
+def test_reference_int4_test_flow_m64(oracle):
+    """tests/python/relax/test_codegen_cutlass.py:1355-1609 with its own shapes (x 64x64, y 128x64):
+    main_bias, main_cast_bias and main_residual against numpy at rtol = atol = 1e-2."""
+    f = np.load(os.path.join(GOLDEN, "ft_int4_percol.npz"))
+    x, y, bias = f["x"], f["y"], f["bias"]
+    rs = np.random.RandomState(1)
+    residual = rs.randn(64, 128).astype(np.float16)
+    pre = ops.preprocess_weight_ft(to_dev(f["packed"]), True, 80)
+    ref = np.dot(x.astype(np.float32), y.astype(np.float32).T) + bias.astype(np.float32)
+    out = ops.gemm_fp16_ft(to_dev(x), pre, to_dev(f["scales"]), 4, bias=to_dev(bias))
+    np.testing.assert_allclose(out.cpu().numpy().astype(np.float32), ref, rtol=1e-2, atol=1e-2)
+    assert_close(out.cpu().numpy(), f["out"], tight=False)
+    out = ops.gemm_fp16_ft(to_dev(x), pre, to_dev(f["scales"]), 4, bias=to_dev(bias), residual=to_dev(residual),
+                           binary_op="plus")
+    np.testing.assert_allclose(out.cpu().numpy().astype(np.float32), ref + residual.astype(np.float32),
+                               rtol=1e-2, atol=1e-2)
