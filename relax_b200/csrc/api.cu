@@ -9,6 +9,7 @@
 #include "gemv.h"
 #include "gemv_cluster.cuh"
 #include "umma_gemv.cuh"
+#include "gemv_sk.cuh"
 #include "gemm_tc.h"
 #include "preprocess.h"
 
@@ -305,13 +306,19 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     }
 #endif
     {
-      // tensor-core (tcgen05) decode kernel where it applies; epoch flags live past the ticket area
+      // epoch flags live past the ticket area of the scratch block
       constexpr size_t kFlagOffset = 49152, kFlagCount = 16384;
+      unsigned* flags = reinterpret_cast<unsigned*>(sc->counters) + kFlagOffset;
       const unsigned epoch = ++sc->epoch;
-      const int rc = umma_gemv_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials,
-                                   sc->partial_bytes, reinterpret_cast<unsigned*>(sc->counters) + kFlagOffset,
-                                   kFlagCount, epoch, stream);
-      if (rc <= 0) return rc;
+      static const int which = getenv("RB200_GEMV_KERNEL") ? atoi(getenv("RB200_GEMV_KERNEL")) : 0;
+      if (which == 0)  // default: warp-MMA consumers on the stream-k split
+        return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
+                           kFlagCount, epoch, stream);
+      if (which == 1) {  // tcgen05 / TMEM variant (kept for batches where its fixed cost amortises)
+        const int rc = umma_gemv_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials,
+                                     sc->partial_bytes, flags, kFlagCount, epoch, stream);
+        if (rc <= 0) return rc;
+      }
     }
     return gemv_cluster_run(p, d->weight_bits, zero_mode(d), sc->sm_count, stream);
   }

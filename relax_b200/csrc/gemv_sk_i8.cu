@@ -1,0 +1,6 @@
+#include "gemv_sk_inst.cuh"
+namespace rb200 {
+namespace sk {
+int launch_sk_i8(const Params& pp, const Launch& l, cudaStream_t stream) { return launch_bits<8>(pp, l, stream); }
+}  // namespace sk
+}  // namespace rb200

@@ -1,0 +1,59 @@
+// Instantiation + dispatch of gemv_sk_kernel for one weight width.
+#pragma once
+#include <cstring>
+
+#include "gemv_sk.cuh"
+
+namespace rb200 {
+namespace sk {
+
+template <int BITS, int MT, int ZMODE, int GROUP, int SRC>
+int launch_inst(const Params& pp, const Launch& l, cudaStream_t stream) {
+  auto kern = gemv_sk_kernel<BITS, MT, ZMODE, GROUP, SRC>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  RB200_CUDA(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    RB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured_device = dev;
+  }
+  kern<<<l.grid, kThreads, l.smem_bytes, stream>>>(pp);
+  RB200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <int BITS, int MT, int ZMODE>
+int launch_gs(const Params& pp, const Launch& l, cudaStream_t stream) {
+#define RB200_CASE(G, S) \
+  if (l.group_code == (G) && l.src == (S)) return launch_inst<BITS, MT, ZMODE, G, S>(pp, l, stream)
+  RB200_CASE(32, kSrcGlobal);
+  RB200_CASE(64, kSrcGlobal);
+  RB200_CASE(128, kSrcGlobal);
+  RB200_CASE(0, kSrcGlobal);
+  RB200_CASE(-1, kSrcGlobal);
+  if (BITS == 4) RB200_CASE(32, kSrcSmemNK);
+  RB200_CASE(32, kSrcSmemKN);
+  RB200_CASE(64, kSrcSmemKN);
+  RB200_CASE(128, kSrcSmemKN);
+#undef RB200_CASE
+  RB200_CHECK(false, "no decode kernel for group code %d with scale source %d", l.group_code, l.src);
+  return -1;
+}
+
+template <int BITS>
+int launch_bits(const Params& pp, const Launch& l, cudaStream_t stream) {
+#define RB200_MZ(M, Z) \
+  if (l.mt == (M) && l.zmode == (Z)) return launch_gs<BITS, M, Z>(pp, l, stream)
+  RB200_MZ(1, kZeroConstInt);
+  RB200_MZ(2, kZeroConstInt);
+  RB200_MZ(4, kZeroConstInt);
+  RB200_MZ(1, kZeroGeneral);
+  RB200_MZ(2, kZeroGeneral);
+  RB200_MZ(4, kZeroGeneral);
+#undef RB200_MZ
+  RB200_CHECK(false, "bad m-tile count %d / zero mode %d", l.mt, l.zmode);
+  return -1;
+}
+
+}  // namespace sk
+}  // namespace rb200

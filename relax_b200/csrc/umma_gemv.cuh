@@ -542,6 +542,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int j = 0; j < 4; ++j) {
               if ((ablate & 4) && !(first && j == 0)) continue;
               const uint64_t bdesc = make_b_desc(xbase + kb * nb * 128 + j * 32);
+              if (ablate & 131072) {  // timing probe: independent accumulators (results are not meaningful)
+                tc_mma_ts(d_col0 + ((kb * 4 + j) % 6) * 16, a_tmem + j * 8, bdesc, idesc, 1u);
+                continue;
+              }
               tc_mma_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
             }
             first = false;
