@@ -310,14 +310,26 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
       constexpr size_t kFlagOffset = 49152, kFlagCount = 16384;
       unsigned* flags = reinterpret_cast<unsigned*>(sc->counters) + kFlagOffset;
       const unsigned epoch = ++sc->epoch;
-      static const int which = getenv("RB200_GEMV_KERNEL") ? atoi(getenv("RB200_GEMV_KERNEL")) : 0;
-      if (which == 0)  // default: warp-MMA consumers on the stream-k split
+      // Which decode kernel: measured crossovers on B200.  Few 128-row tiles (n <= 4096): the
+      // cluster kernel, whose split-k partials meet in distributed shared memory, beats the
+      // global slot + flag fix-up by about 3 us.  Otherwise the stream-k warp-MMA kernel; for
+      // 17..32 rows on large weights the tcgen05 kernel (one MMA covers the whole batch).
+      static const int forced = getenv("RB200_GEMV_KERNEL") ? atoi(getenv("RB200_GEMV_KERNEL")) : -1;
+      const long long wbytes = (long long)p.n * p.k * d->weight_bits / 8;
+      int which = 0;
+      if (p.m > 16 && wbytes >= (40ll << 20)) which = 1;
+      else if (p.n <= 4096) which = 2;
+      if (forced >= 0) which = forced;
+      if (which == 0)
         return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
                            kFlagCount, epoch, stream);
-      if (which == 1) {  // tcgen05 / TMEM variant (kept for batches where its fixed cost amortises)
+      if (which == 1) {
         const int rc = umma_gemv_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials,
                                      sc->partial_bytes, flags, kFlagCount, epoch, stream);
-        if (rc <= 0) return rc;
+        if (rc < 0) return rc;
+        if (rc == 0) return 0;
+        return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
+                           kFlagCount, epoch, stream);
       }
     }
     return gemv_cluster_run(p, d->weight_bits, zero_mode(d), sc->sm_count, stream);

@@ -176,6 +176,11 @@ __global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(cons
   fence_proxy_async();
   __syncthreads();
 
+#ifdef RB200_ABLATE
+  const int ablate = p.ablate;
+#else
+  constexpr int ablate = 0;
+#endif
   const long long total = p.total_iters;
   const long long grid = gridDim.x;
   const long long it0 = range_start(blockIdx.x, total, grid);
@@ -351,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(cons
       }
       const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
       const uint8_t* sbase = smem + (size_t)stage * kStage;
-      if (active) {
+      if (active && !(ablate & 4)) {
         const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * (nkb * kTileBytes)) + unit;
         const uint8_t* xsm = sbase + G::kWBytes + g * G::kXPitch + t * (G::kFrag / 2);
         uint4 nk_s_g, nk_s_g8, nk_z_g, nk_z_g8;
@@ -414,13 +419,24 @@ __global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(cons
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint32_t a[4];
-                decode_int4_word<ZMODE>(ww[j], zc, s_g, s_g8, z_g, z_g8, a);
+                if (ablate & 1) {
+                  a[0] = ww[j]; a[1] = ww[j] ^ s_g; a[2] = ww[j] + s_g8; a[3] = ww[j] | z_g;
+                } else {
+                  decode_int4_word<ZMODE>(ww[j], zc, s_g, s_g8, z_g, z_g8, a);
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                   const uint4& xr = xv[mt][j >> 1];
                   const uint32_t b0 = (j & 1) ? xr.z : xr.x;
                   const uint32_t b1 = (j & 1) ? xr.w : xr.y;
-                  mma_16816(acc[mt][j % kChains], a, b0, b1);
+                  if (ablate & 2) {
+                    acc[mt][j % kChains][0] += __uint_as_float(a[0] ^ b0);
+                    acc[mt][j % kChains][1] += __uint_as_float(a[1] ^ b1);
+                    acc[mt][j % kChains][2] += __uint_as_float(a[2]);
+                    acc[mt][j % kChains][3] += __uint_as_float(a[3]);
+                  } else {
+                    mma_16816(acc[mt][j % kChains], a, b0, b1);
+                  }
                 }
               }
             } else {
