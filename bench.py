@@ -68,7 +68,7 @@ def cpu_sample(target_seconds: float):
     g = np.random.Generator(np.random.PCG64(1000))
     cases = {}
     for name, k, n in linears():
-        rows = min(n, 2048)
+        rows = min(n, 4096)
         cases[name] = synth.q4_case(g, max(MS), k, rows, GROUP)
     # probe: 256 rows of every linear at every M
     t0 = time.perf_counter()
@@ -77,7 +77,7 @@ def cpu_sample(target_seconds: float):
         for m in MS:
             C.baseline_q4_nk(c.x[:m], c.w, c.scales, GROUP, 0, 256)
     probe = time.perf_counter() - t0
-    rows = int(max(16, min(2048, 256 * target_seconds / max(probe, 1e-6)))) // 16 * 16
+    rows = int(max(16, min(4096, 256 * target_seconds / max(probe, 1e-6)))) // 16 * 16
 
     def run_once():
         t = time.perf_counter()
@@ -379,7 +379,8 @@ def run_gpu(args):
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "gemv_kernel", "per_shape_gbs": shape_gbs},
+                         "kernel": "gemv_sk_kernel / gemv_cluster_kernel / umma_gemv_kernel (chosen per shape)",
+                         "per_shape_gbs": shape_gbs},
             "cpu_baseline": cpu,
             "clocks": {"sm_mhz": clk["sm_mhz"], "sm_max_mhz": clk["sm_max_mhz"], "reasons": clk["reasons"]},
             "max_rel_err_vs_oracle": max_rel_err,

@@ -1,18 +1,42 @@
-// m > 32: batch-sliced execution on the tensor-core decode kernel.
-//
-// The decode kernel takes the batch as the MMA's N dimension (up to 32 rows per pass).  Larger
-// batches are run as consecutive 32-row slices, each a full pass over the packed weight; the
-// weight (tens of MB) stays L2-resident between passes for the layer sizes of the benchmark
-// configurations.  A dedicated prefill kernel with a 256-row batch tile replaces this path;
-// until then this keeps every entry point correct for any m.
+// m > 32: the tcgen05 prefill kernel (256-row batch tiles, weights decoded into tensor memory);
+// shapes it does not cover (n not a multiple of 128, k not a multiple of 64, unaligned x) run as
+// consecutive 32-row batch slices on the decode kernel, each a full pass over the packed weight.
 #include "gemm_tc.h"
+
+#include <cstring>
+
+#include "umma_gemm.cuh"
 
 namespace rb200 {
 
-int gemm_tc_launch(const rb200_gemm_desc* d, const Epilogue&, int, int, cudaStream_t stream) {
-  rb200_gemm_desc s = *d;
+int gemm_tc_launch(const rb200_gemm_desc* d, const Epilogue& epi, int group, int zmode, cudaStream_t stream) {
   const int64_t ldx = d->ldx > 0 ? d->ldx : d->k;
   const int64_t ldo = d->ldo > 0 ? d->ldo : d->n;
+  DeviceScratch* sc = device_scratch(0, 0);
+  if (!sc) return -1;
+  {
+    GemvParams p;
+    memset(&p, 0, sizeof(p));
+    p.status = sc->status;
+    p.x = static_cast<const __half*>(d->x);
+    p.ldx = ldx;
+    p.w = static_cast<const uint8_t*>(d->w);
+    p.s = static_cast<const __half*>(d->scales);
+    p.z = static_cast<const __half*>(d->zeros);
+    p.s_n = d->scale_stride_n;
+    p.s_g = d->scale_stride_g;
+    p.out = static_cast<__half*>(d->out);
+    p.ldo = ldo;
+    p.epi = epi;
+    p.m = (int)d->m;
+    p.n = (int)d->n;
+    p.k = (int)d->k;
+    p.group = group;
+    p.zero_const = d->zero_const;
+    const int rc = umma_gemm_run(p, d->weight_bits, zmode, sc->sm_count, stream);
+    if (rc <= 0) return rc;
+  }
+  rb200_gemm_desc s = *d;
   for (int64_t m0 = 0; m0 < d->m; m0 += 32) {
     s.m = (d->m - m0) < 32 ? (d->m - m0) : 32;
     s.x = static_cast<const char*>(d->x) + m0 * ldx * 2;

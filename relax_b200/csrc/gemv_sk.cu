@@ -51,8 +51,7 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
 
   static const int env_stages = getenv("RB200_GEMV_STAGES") ? atoi(getenv("RB200_GEMV_STAGES")) : 0;
   static const int env_ctas = getenv("RB200_GEMV_CTAS_PER_SM") ? atoi(getenv("RB200_GEMV_CTAS_PER_SM")) : 0;
-  // four m-tiles need the register file of a whole SM: one CTA per SM, deeper pipeline
-  const int ctas_per_sm = env_ctas > 0 ? env_ctas : (l.mt == 4 ? 1 : 2);
+  const int ctas_per_sm = env_ctas > 0 ? env_ctas : 2;
   const int xpitch = chunk * 2 + (bits == 4 ? 16 : 64);
   size_t sb = (size_t)kConsumerWarps * kBlocksPerChunk * kTileBytes + (size_t)((l.mt * 8 * xpitch + 127) / 128) * 128;
   if (l.src != kSrcGlobal) sb += kScaleBoxBytes * (zmode == kZeroGeneral ? 2 : 1);
@@ -67,7 +66,7 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   if (grid > p.total_iters) grid = p.total_iters;
   l.grid = (int)grid;
 
-  const size_t need = (size_t)l.grid * kConsumerWarps * l.mt * 128 * sizeof(float);
+  const size_t need = (size_t)l.grid * 2 * kConsumerWarps * l.mt * 128 * sizeof(float);
   RB200_CHECK(partial_bytes >= need && flag_count >= (size_t)l.grid * kConsumerWarps,
               "split-k scratch too small: need %zu bytes and %d flags", need, l.grid * kConsumerWarps);
   pp.partial = partial;

@@ -60,7 +60,7 @@ struct StageLayout {
 
 struct Params {
   GemvParams g;
-  float* partial;     // [grid][8 warps][MT][4][32] fp32 tail pieces
+  float* partial;     // [grid][2][8 warps][MT][4][32] fp32: slot 0 tail piece (for the owner), slot 1 own head piece
   unsigned* flags;    // [grid][8] epoch flags, one per consumer warp
   unsigned epoch;
   int has_z_tile;
@@ -145,7 +145,7 @@ struct ScalePlan {
 };
 
 template <int BITS, int MT, int ZMODE, int GROUP, int SRC>
-__global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(const Params pp) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   using G = Geo<BITS>;
   using L = StageLayout<BITS, MT, ZMODE, SRC>;
   using SP = ScalePlan<BITS, GROUP>;
@@ -288,7 +288,10 @@ __global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(cons
   const int unit = frag_unit_pos(lane);
 
   float acc[MT][kChains][4];
-  float head[MT][4];     // the head piece waits here for the other CTAs' parts
+  // the head piece waits for the other CTAs' parts: in registers for one or two m-tiles, in this
+  // CTA's own global slot for four (the register file then fits two CTAs per SM)
+  constexpr bool kHeadInRegs = MT <= 2;
+  float head[kHeadInRegs ? MT : 1][4];
   bool have_head = false;
   int head_tile = 0;
   uint32_t s_cur[SP::kCount], s_nxt[SP::kCount];
@@ -408,16 +411,15 @@ __global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(cons
               }
             }
             if (BITS == 4) {
+              const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
               uint4 xv[MT][2];
 #pragma unroll
-              for (int mt = 0; mt < MT; ++mt) {
-                const uint4* xp = reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 128);
-                xv[mt][0] = xp[0];
-                xv[mt][1] = xp[1];
-              }
-              const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
               for (int j = 0; j < 4; ++j) {
+                if ((j & 1) == 0) {
+#pragma unroll
+                  for (int mt = 0; mt < MT; ++mt)
+                    xv[mt][j >> 1] = *reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 128 + (j >> 1) * 16);
+                }
                 uint32_t a[4];
                 if (ablate & 1) {
                   a[0] = ww[j]; a[1] = ww[j] ^ s_g; a[2] = ww[j] + s_g8; a[3] = ww[j] | z_g;
@@ -481,13 +483,21 @@ __global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(cons
     } else if (pc.kind == kHead) {
       have_head = true;
       head_tile = pc.tile;
+      if (kHeadInRegs) {
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+        for (int mt = 0; mt < (kHeadInRegs ? MT : 1); ++mt)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) head[mt][c] = fin[mt][c];
+          for (int c = 0; c < 4; ++c) head[mt][c] = fin[mt][c];
+      } else {
+        float* dst = pp.partial + ((size_t)((blockIdx.x * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) dst[mt * 128 + c * 32] = fin[mt][c];
+      }
     } else {
       // tail piece: publish for the owner (the CTA that holds this tile's first chunk)
-      float* dst = pp.partial + ((size_t)(blockIdx.x * kConsumerWarps + warp) * MT) * 128 + lane;
+      float* dst = pp.partial + ((size_t)((blockIdx.x * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -516,14 +526,27 @@ __global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2) gemv_sk_kernel(cons
     }
     flags_ok = __all_sync(0xffffffffu, flags_ok);
     if (flags_ok) {
-      for (int c = blockIdx.x + 1; c <= last_cta; ++c) {  // fixed CTA order: deterministic
-        const float* src = pp.partial + ((size_t)(c * kConsumerWarps + warp) * MT) * 128 + lane;
+      float sum[MT][4];
+      if (kHeadInRegs) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) head[mt][cc] += __ldcg(src + mt * 128 + cc * 32);
+          for (int cc = 0; cc < 4; ++cc) sum[mt][cc] = head[kHeadInRegs ? mt : 0][cc];
+      } else {
+        const float* own = pp.partial + ((size_t)((blockIdx.x * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) sum[mt][cc] = own[mt * 128 + cc * 32];  // written by this same thread
       }
-      store_tile(head, head_tile);
+      for (int c = blockIdx.x + 1; c <= last_cta; ++c) {  // fixed CTA order: deterministic
+        const float* src = pp.partial + ((size_t)((c * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) sum[mt][cc] += __ldcg(src + mt * 128 + cc * 32);
+      }
+      store_tile(sum, head_tile);
     }
   }
 }

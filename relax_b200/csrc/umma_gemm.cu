@@ -1,0 +1,74 @@
+// Host side of the tcgen05 prefill kernel: coverage test, tile plan, x tensor map, dispatch.
+#include "umma_gemm.cuh"
+
+#include <cstdlib>
+#include <cstring>
+
+#include "tensormap.h"
+
+namespace rb200 {
+
+int umma_gemm_run(const GemvParams& p_in, int bits, int zmode, int sm_count, cudaStream_t stream) {
+  using namespace um;
+  // coverage: whole 128-row tiles, whole 64-k blocks, TMA-loadable x
+  if (p_in.n % kTileRows != 0 || p_in.k % kKBlock != 0) return 1;
+  if ((reinterpret_cast<uintptr_t>(p_in.x) & 15u) != 0 || (p_in.ldx * 2) % 16 != 0) return 1;
+  static const bool disabled = getenv("RB200_GEMM_NO_TCGEN05") != nullptr;
+  if (disabled) return 1;
+
+  Params pp;
+  memset(&pp, 0, sizeof(pp));
+  pp.g = p_in;
+  GemvParams& p = pp.g;
+  // balanced batch tiles of at most 256 rows, padded to the 32 rows the epilogue split needs
+  pp.m_tiles = (p.m + kMaxNb - 1) / kMaxNb;
+  pp.nb = (((p.m + pp.m_tiles - 1) / pp.m_tiles) + 31) / 32 * 32;
+
+  Launch l;
+  l.zmode = zmode;
+  if (p.group <= 0 || p.group >= p.k) {
+    l.group_code = 0;
+  } else {
+    RB200_CHECK(p.group % 16 == 0 && p.k % p.group == 0,
+                "group_size=%d must divide k=%d and be a multiple of 16", p.group, p.k);
+    l.group_code = (bits == 4 && (p.group == 32 || p.group == 64 || p.group == 128)) ? p.group : -1;
+  }
+  l.src = ug::kSrcGlobal;
+  const int64_t kg = l.group_code != 0 ? p.k / p.group : 0;
+  const bool al = (reinterpret_cast<uintptr_t>(p.s) & 15u) == 0 &&
+                  (p.z == nullptr || (reinterpret_cast<uintptr_t>(p.z) & 15u) == 0);
+  if (bits == 4 && l.group_code > 0 && al) {
+    if (p.s_g == 1 && p.s_n == kg && p.group == 32 && (kg * 2) % 16 == 0) l.src = ug::kSrcSmemNK;
+    else if (p.s_n == 1 && p.s_g == p.n && (p.n * 2) % 16 == 0) l.src = ug::kSrcSmemKN;
+  }
+  if (l.src != ug::kSrcGlobal && zmode == kZeroGeneral && p.z) pp.has_z_tile = 1;
+
+  const long long total_tiles = (long long)(p.n / kTileRows) * pp.m_tiles;
+  static const int env_grid = getenv("RB200_GEMM_GRID") ? atoi(getenv("RB200_GEMM_GRID")) : 0;
+  long long grid = sm_count;  // one persistent CTA per SM (a tensor-memory kernel gets occupancy 1)
+  if (env_grid > 0) grid = env_grid;
+  if (grid > total_tiles) grid = total_tiles;
+  l.grid = (int)grid;
+
+  const size_t budget = (size_t)227 * 1024;
+  int xs = kMaxXStages;
+  while (xs > 2 && smem_bytes(pp.nb, xs) > budget) --xs;
+  static const int env_xs = getenv("RB200_GEMM_X_STAGES") ? atoi(getenv("RB200_GEMM_X_STAGES")) : 0;
+  if (env_xs >= 2 && env_xs <= xs) xs = env_xs;
+  pp.x_stages = xs;
+  l.smem = smem_bytes(pp.nb, xs);
+
+  CUtensorMap tx;
+  if (make_tensor_map_2d(&tx, p.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (unsigned long long)p.k,
+                         (unsigned long long)p.m, (unsigned long long)p.ldx * 2, kKBlock, (unsigned)pp.nb,
+                         CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return -1;
+
+  if (bits == 4) {
+    if (zmode == kZeroConstInt) return launch_gemm_i4c(pp, l, tx, stream);
+    return launch_gemm_i4g(pp, l, tx, stream);
+  }
+  return launch_gemm_i8(pp, l, tx, stream);
+}
+
+}  // namespace rb200

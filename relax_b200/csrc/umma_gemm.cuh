@@ -1,0 +1,472 @@
+// Prefill kernel (m > 32): dense contraction on the 5th-generation tensor cores.
+//
+//   out^T tile [128 weight rows x up to 256 batch rows] = W_tile [128 x K] * x_tile^T [K x 256]
+//
+// tcgen05.mma (kind::f16, M = 128, K = 16) costs about 172 clocks per instruction on B200
+// whatever its N, so the batch is the instruction's N and is made as wide as it goes (256): one
+// instruction then does 128 x 256 x 16 MACs.  The dequantised weights are the A operand and never
+// touch shared memory: decode warps write them straight into tensor memory (tcgen05.st), the MMA
+// reads A from TMEM and B (= x) from a 128B-swizzled K-major tile in shared memory, the fp32
+// accumulator sits in 256 TMEM columns.
+//
+//   warp 0 (producer)  : packed weights, one 16 KB bulk copy per (128-row tile, 4 fragment tiles)
+//   warp 1 (MMA)       : one thread, 4 x tcgen05.mma per 64-k block; commits recycle A buffers
+//                        and x stages; the commit after the last block hands over the accumulator
+//   warp 2 (scales)    : scale / zero tiles of the chunk with 16-byte cp.async (when staged)
+//   warp 3 (x)         : one TMA tile load per 64-k block: box 64 k x nb batch rows, 128-byte
+//                        swizzle = the tensor core's K-major operand layout; rows past m read zero
+//   warps 4..11        : two groups of four warps (128 TMEM lanes each) decode alternate 64-k
+//                        blocks; thread = weight row; bit-exact decode, tcgen05.st into one of
+//                        four 32-column A buffers.  After the last block the same warps drain
+//                        the accumulator (group 0: batch columns [0, nb/2), group 1: the rest),
+//                        apply bias / activation / residual, round once to fp16 and store.
+// Tiles are walked persistently, batch tiles fastest, so CTAs running together share a weight
+// tile in L2.  Every wait is bounded and reports through the device status word.
+//
+// Stands in for fastertransformer::gemm_fp16_int_bias_act[_residual] at large m
+// (python/tvm/contrib/cutlass/gemm_operation.py:441-458) and the reference's tensor-core matmul
+// schedule (python/tvm/dlight/gpu/matmul.py:316-535).
+#pragma once
+
+#include <cuda.h>
+
+#include "dequant.cuh"
+#include "gemv.h"
+#include "gemv_cluster.cuh"
+#include "umma_gemv.cuh"
+
+namespace rb200 {
+namespace um {
+
+constexpr int kDecodeWarps = 8;
+constexpr int kFirstDecodeWarp = 4;
+constexpr int kThreads = (kFirstDecodeWarp + kDecodeWarps) * 32;
+constexpr int kTileRows = 128;
+constexpr int kKBlock = 64;                 // k per MMA block (4 x K=16)
+constexpr int kWBytes = 8 * 4 * 512;        // one weight stage: 8 row blocks x 4 fragment tiles
+constexpr int kScaleBoxBytes = 2048;
+constexpr int kWStageBytes = kWBytes + 2 * kScaleBoxBytes;
+constexpr int kWStages = 3;
+constexpr int kMaxXStages = 8;
+constexpr int kNumA = 4;                    // TMEM A buffers of 32 columns (one 64-k block each)
+constexpr int kTmemCols = 512;
+constexpr int kDCols = 256;                 // accumulator: columns [0, 256); A buffers follow
+constexpr int kMaxNb = 256;
+
+struct Params {
+  GemvParams g;
+  int nb;          // batch rows per tile = MMA N (multiple of 32, <= 256)
+  int m_tiles;
+  int x_stages;
+  int has_z_tile;
+};
+
+inline size_t smem_bytes(int nb, int x_stages) {
+  return 1024 + (size_t)x_stages * nb * 128 + (size_t)kWStages * kWStageBytes +
+         (size_t)(2 * kWStages + 2 * kMaxXStages + 2 * kNumA + 2) * 8 + 16;
+}
+
+#ifdef __CUDACC__
+
+using gc::tma_load_2d;
+using ug::cp_async16;
+using ug::cp_async_arrive;
+using ug::kSrcGlobal;
+using ug::kSrcSmemKN;
+using ug::kSrcSmemNK;
+using ug::make_b_desc;
+using ug::RowCtx;
+using ug::tc_commit;
+using ug::tc_fence_after;
+using ug::tc_fence_before;
+using ug::tc_ld16;
+using ug::tc_mma_ts;
+using ug::tc_st32;
+using ug::tc_wait_st;
+using ug::tmem_alloc;
+using ug::tmem_dealloc;
+using ug::tmem_relinquish;
+
+// int8: one 64-k MMA block = two 32-k fragment tiles.  Unit (g, t) of a tile holds, for row
+// g + 8 HI, the words 2j + HI (j = 0, 1) = k 8t + 4j .. + 3 in byte order.
+template <int ZMODE, int GROUP, int HI, int KBM>
+__device__ __forceinline__ void decode_block8(const GemvParams& p, const RowCtx& c, const ZeroConsts& zc,
+                                              uint32_t zconst_h2, int group, uint32_t (&regs)[32]) {
+  constexpr uint32_t kMagicBytes = 0x64646464u;
+#pragma unroll
+  for (int ti = 0; ti < 2; ++ti) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const uint4 u = *reinterpret_cast<const uint4*>(c.wblk + (KBM * 2 + ti) * 512 + c.unit_off[t]);
+      uint32_t s2, z2 = zconst_h2;
+      if (GROUP == 0) {
+        s2 = c.s_chan;
+        z2 = c.z_chan;
+      } else {
+        const int64_t kk = (int64_t)(c.kb0 + KBM) * kKBlock + ti * 32 + t * 8;
+        const int64_t o = c.n_row * p.s_n + (kk / group) * p.s_g;
+        s2 = h2_bcast(p.s[o]);
+        if (ZMODE == kZeroGeneral && p.z) z2 = h2_bcast(p.z[o]);
+      }
+      const uint32_t w0 = HI ? u.y : u.x, w1 = HI ? u.w : u.z;
+      const uint32_t ww[2] = {w0, w1};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint32_t e0 = h2_sub(prmt(ww[j], kMagicBytes, 0x4140u), zc.sub_lo);
+        uint32_t e1 = h2_sub(prmt(ww[j], kMagicBytes, 0x4342u), zc.sub_lo);
+        if (ZMODE == kZeroGeneral) {
+          e0 = h2_sub(e0, z2);
+          e1 = h2_sub(e1, z2);
+        }
+        regs[16 * ti + 4 * t + 2 * j] = h2_mul(e0, s2);
+        regs[16 * ti + 4 * t + 2 * j + 1] = h2_mul(e1, s2);
+      }
+    }
+  }
+}
+
+template <int BITS, int ZMODE, int GROUP, int SRC, int HI>
+__device__ __forceinline__ void decode_any(int kbm, const GemvParams& p, const ug::Params& up, const RowCtx& c,
+                                           const ZeroConsts& zc, uint32_t zconst_h2, int group,
+                                           uint32_t (&regs)[32]) {
+  if constexpr (BITS == 4) {
+    ug::decode_block_kb<ZMODE, GROUP, SRC, HI>(kbm, p, up, c, zc, zconst_h2, group, regs);
+  } else {
+    if (kbm == 0) decode_block8<ZMODE, GROUP, HI, 0>(p, c, zc, zconst_h2, group, regs);
+    else decode_block8<ZMODE, GROUP, HI, 1>(p, c, zc, zconst_h2, group, regs);
+  }
+}
+
+template <int BITS, int ZMODE, int GROUP, int SRC>
+__global__ void __launch_bounds__(kThreads, 1)
+    umma_gemm_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_x) {
+  constexpr int kTilesPerBlock = BITS == 4 ? 1 : 2;       // fragment tiles per 64-k MMA block
+  constexpr int kBlocksPerChunk = 4 / kTilesPerBlock;     // MMA blocks per weight stage
+  constexpr int kFragK = BITS == 4 ? 64 : 32;
+  extern __shared__ uint8_t smem_raw[];
+  const GemvParams& p = pp.g;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int nb = pp.nb;
+  const int x_stages = pp.x_stages;
+  const int x_stage_bytes = nb * 128;
+  uint8_t* x_ring = smem;
+  uint8_t* w_ring = smem + (size_t)x_stages * x_stage_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(w_ring + (size_t)kWStages * kWStageBytes);
+  uint64_t* w_full = bars;
+  uint64_t* w_empty = w_full + kWStages;
+  uint64_t* x_full = w_empty + kWStages;
+  uint64_t* x_empty = x_full + kMaxXStages;
+  uint64_t* a_full = x_empty + kMaxXStages;
+  uint64_t* a_empty = a_full + kNumA;
+  uint64_t* d_full = a_empty + kNumA;
+  uint64_t* d_empty = d_full + 1;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_empty + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < kWStages; ++s) {
+      mbar_init(&w_full[s], 1 + (SRC != kSrcGlobal ? 32 : 0));  // expect_tx arrival (+ scale loader lanes)
+      mbar_init(&w_empty[s], kDecodeWarps);
+    }
+    for (int s = 0; s < x_stages; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&x_empty[s], 1);
+    }
+    for (int i = 0; i < kNumA; ++i) {
+      mbar_init(&a_full[i], 4);
+      mbar_init(&a_empty[i], 1);
+    }
+    mbar_init(d_full, 1);
+    mbar_init(d_empty, kDecodeWarps);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t d_col0 = tmem_base;
+  const uint32_t a_col0 = tmem_base + kDCols;
+
+  const int kb_total = p.k / kKBlock;             // MMA blocks along k
+  const int ft_total = p.k / kFragK;              // fragment tiles along k
+  const int chunks = (ft_total + 3) / 4;          // weight stages per tile
+  const int n_tiles = p.n / kTileRows;
+  const int total_tiles = n_tiles * pp.m_tiles;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ============================================================ producer: packed weights
+    int ws = 0;
+    uint32_t wph = 0;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      const int n_tile = t / pp.m_tiles;
+      for (int chunk = 0; chunk < chunks; ++chunk) {
+        if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          const int nft = min(4, ft_total - chunk * 4);
+          const uint32_t wbytes = (uint32_t)nft * 8 * 512;
+          mbar_arrive_expect_tx(&w_full[ws], wbytes);
+          bulk_g2s(w_ring + (size_t)ws * kWStageBytes, p.w + frag_stage_offset(n_tile, chunk, p.n / 16, ft_total),
+                   wbytes, &w_full[ws]);
+        }
+        __syncwarp();
+        if (++ws == kWStages) {
+          ws = 0;
+          wph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer (one thread)
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(nb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      int xs = 0;
+      uint32_t xph = 0;
+      uint32_t q = 0;       // running 64-k block counter (selects the A buffer)
+      uint32_t tile_i = 0;  // tiles done by this CTA
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
+        if (!mbar_wait_parked(d_empty, (tile_i & 1u) ^ 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < kb_total; ++kb, ++q) {
+          if (!mbar_wait_parked(&x_full[xs], xph, p.status)) {
+            ok = false;
+            break;
+          }
+          const uint32_t ab = q % kNumA;
+          if (!mbar_wait_parked(&a_full[ab], (q / kNumA) & 1u, p.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t xbase = smem_u32(x_ring + (size_t)xs * x_stage_bytes);
+          const uint32_t a_tmem = a_col0 + ab * 32;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == 0 && j == 0) ? 0u : 1u);
+          tc_commit(&a_empty[ab]);
+          tc_commit(&x_empty[xs]);
+          if (++xs == x_stages) {
+            xs = 0;
+            xph ^= 1u;
+          }
+        }
+        if (ok) tc_commit(d_full);
+      }
+    }
+  } else if (warp == 2) {
+    // ============================================================ scale / zero tiles of each chunk
+    if (SRC != kSrcGlobal) {
+      int ws = 0;
+      uint32_t wph = 0;
+      const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const int64_t n0 = (int64_t)(t / pp.m_tiles) * kTileRows;
+        for (int chunk = 0; chunk < chunks; ++chunk) {
+          if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* wsb = w_ring + (size_t)ws * kWStageBytes;
+          if (SRC == kSrcSmemNK) {
+            // [128 rows][8 groups of 32]: 16 bytes per row, four rows per lane
+            const int64_t g0 = (int64_t)chunk * 8;
+            const int64_t left = (kg - g0) * 2;
+            const uint32_t sv = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int row = lane + 32 * i;
+              const int64_t o = (n0 + row) * kg + (sv ? g0 : 0);
+              cp_async16(wsb + kWBytes + row * 16, p.s + o, sv);
+              if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(wsb + kWBytes + kScaleBoxBytes + row * 16, p.z + o, sv);
+            }
+          } else {
+            // [groups of the chunk][128 rows]: 256 bytes per group row
+            constexpr int kG = GROUP > 0 ? (256 / GROUP) : 1;
+            for (int i = lane; i < kG * 16; i += 32) {
+              const int gl = i >> 4, cc = i & 15;
+              const int64_t grow = (int64_t)chunk * kG + gl;
+              const uint32_t sv = grow < kg ? 16u : 0u;
+              const int64_t o = (sv ? grow : 0) * p.n + n0 + cc * 8;
+              cp_async16(wsb + kWBytes + gl * 256 + cc * 16, p.s + o, sv);
+              if (ZMODE == kZeroGeneral && pp.has_z_tile)
+                cp_async16(wsb + kWBytes + kScaleBoxBytes + gl * 256 + cc * 16, p.z + o, sv);
+            }
+          }
+          cp_async_arrive(&w_full[ws]);
+          if (++ws == kWStages) {
+            ws = 0;
+            wph ^= 1u;
+          }
+        }
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");
+    }
+  } else if (warp == 3) {
+    // ============================================================ x tiles (TMA)
+    int xs = 0;
+    uint32_t xph = 0;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      const int m0 = (t % pp.m_tiles) * nb;
+      for (int kb = 0; kb < kb_total; ++kb) {
+        if (!mbar_wait_parked(&x_empty[xs], xph ^ 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
+          tma_load_2d(x_ring + (size_t)xs * x_stage_bytes, &tmap_x, kb * kKBlock, m0, &x_full[xs]);
+        }
+        __syncwarp();
+        if (++xs == x_stages) {
+          xs = 0;
+          xph ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ============================================================ decode + epilogue warps
+    const int dw = warp - kFirstDecodeWarp;
+    const int grp = dw >> 2;
+    const int w4 = warp & 3;             // TMEM lane quadrant of this warp
+    const int hi = w4 & 1;               // rows g (0) or g+8 (1) of the 16-row blocks
+    const int bl = (w4 >> 1) * 4 + (lane >> 3);
+    const int g = lane & 7;
+    const int row = 16 * bl + g + 8 * hi;
+    const uint32_t lane_taddr = (uint32_t)(32 * w4) << 16;
+    const ZeroConsts zc = make_zero_consts(ZMODE, p.zero_const);
+    const uint32_t zconst_h2 = h2_bcast(__float2half_rn(p.zero_const));
+    const int group = GROUP > 0 ? GROUP : (GROUP == 0 ? p.k : p.group);
+    uint32_t unit_off[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) unit_off[t] = (uint32_t)(t * 128 + ((g + 2 * t) & 7) * 16);
+    ug::Params up;  // the int4 block decoder reads only has_z_tile from it
+    up.has_z_tile = pp.has_z_tile;
+
+    int ws = 0;
+    uint32_t wph = 0;
+    uint32_t q = 0;
+    uint32_t tile_i = 0;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
+      const int n_tile = t / pp.m_tiles, m_tile = t % pp.m_tiles;
+      const int64_t n_row = (int64_t)n_tile * kTileRows + row;
+      uint32_t s_chan = 0, z_chan = zconst_h2;
+      if (GROUP == 0) {
+        s_chan = h2_bcast(p.s[n_row * p.s_n]);
+        if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row * p.s_n]);
+      }
+      for (int chunk = 0; chunk < chunks && ok; ++chunk) {
+        if (!mbar_wait_parked(&w_full[ws], wph, p.status)) {
+          ok = false;
+          break;
+        }
+        const int nft = min(4, ft_total - chunk * 4);
+        const int nblk = nft / kTilesPerBlock;
+        const uint8_t* wsb = w_ring + (size_t)ws * kWStageBytes;
+        RowCtx c;
+        c.wblk = wsb + bl * (nft * 512);
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) c.unit_off[tt] = unit_off[tt];
+        c.s_tile = wsb + kWBytes;
+        c.z_tile = wsb + kWBytes + kScaleBoxBytes;
+        c.nk_s = make_uint4(0, 0, 0, 0);
+        c.nk_z = make_uint4(0, 0, 0, 0);
+        if (SRC == kSrcSmemNK) {
+          c.nk_s = *reinterpret_cast<const uint4*>(c.s_tile + row * 16);
+          if (ZMODE == kZeroGeneral && pp.has_z_tile) c.nk_z = *reinterpret_cast<const uint4*>(c.z_tile + row * 16);
+        }
+        c.s_chan = s_chan;
+        c.z_chan = z_chan;
+        c.row = row;
+        c.n_row = n_row;
+        c.kb0 = chunk * kBlocksPerChunk;
+#pragma unroll 1
+        for (int kbm = 0; kbm < nblk; ++kbm, ++q) {
+          if ((int)(q & 1u) != grp) continue;
+          const uint32_t ab = q % kNumA;
+          if (!mbar_wait_parked(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t regs[32];
+          if (hi) decode_any<BITS, ZMODE, GROUP, SRC, 1>(kbm, p, up, c, zc, zconst_h2, group, regs);
+          else decode_any<BITS, ZMODE, GROUP, SRC, 0>(kbm, p, up, c, zc, zconst_h2, group, regs);
+          tc_st32(lane_taddr | (a_col0 + ab * 32), regs);
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[ab]);
+        }
+        if (!ok) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&w_empty[ws]);
+        if (++ws == kWStages) {
+          ws = 0;
+          wph ^= 1u;
+        }
+      }
+      if (!ok) break;
+      // ---------------------------------------------------------- epilogue of this tile
+      if (!mbar_wait_parked(d_full, tile_i & 1u, p.status)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int64_t m0 = (int64_t)m_tile * nb;
+      const int c_begin = grp * (nb / 2), c_end = c_begin + nb / 2;
+      for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+        if (m0 + c0 >= p.m) break;
+        float v[16];
+        tc_ld16(lane_taddr | (d_col0 + c0), v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int64_t m = m0 + c0 + i;
+          if (m < p.m) p.out[m * p.ldo + n_row] = __float2half_rn(apply_epilogue(v[i], p.epi, m, n_row));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_empty);
+    }
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+#endif  // __CUDACC__
+
+struct Launch {
+  int grid;
+  size_t smem;
+  int group_code;
+  int src;
+  int zmode;
+};
+int launch_gemm_i4c(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream);
+int launch_gemm_i4g(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream);
+int launch_gemm_i8(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream);
+
+}  // namespace um
+
+// Host entry: returns 1 when the problem is outside this kernel's coverage (the caller then runs
+// batch slices on the decode kernel), 0 on launch, -1 on error.
+int umma_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, cudaStream_t stream);
+
+}  // namespace rb200
