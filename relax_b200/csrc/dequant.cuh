@@ -199,5 +199,46 @@ __device__ __forceinline__ float apply_epilogue(float v, const Epilogue& e, int6
   return v;
 }
 
+// Same, for 16 consecutive batch rows m_base .. m_base + 15 of one output column n (rows >= m_end
+// are padding: nothing is loaded for them).  The operand tests sit outside the element loops so
+// that the plain case costs one add per element and no transcendental code is ever executed
+// speculatively.
+__device__ __forceinline__ void apply_epilogue16(float (&v)[16], const Epilogue& e, int64_t m_base, int64_t m_end,
+                                                 int64_t n) {
+  if (e.bias) {
+    if (e.bias_stride == 0) {
+      const float b = __half2float(e.bias[n]);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] += b;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (m_base + i < m_end) v[i] += __half2float(e.bias[(m_base + i) * e.bias_stride + n]);
+    }
+  }
+  if (e.act == 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.0f);
+  } else if (e.act == 2) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.0f + __expf(-v[i]));
+  } else if (e.act == 3) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.5f * v[i] * (1.0f + erff(v[i] * 0.70710678118654752f));
+  }
+  if (e.residual) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (m_base + i < m_end) {
+        const float r = __half2float(e.residual[(m_base + i) * e.ld_res + n]);
+        v[i] = e.binop == 2 ? v[i] * r : v[i] + r;
+      }
+  }
+  if (e.unop == 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.0f);
+  }
+}
+
 #endif  // __CUDACC__
 }  // namespace rb200

@@ -3,6 +3,7 @@
 // consecutive 32-row batch slices on the decode kernel, each a full pass over the packed weight.
 #include "gemm_tc.h"
 
+#include <cstdlib>
 #include <cstring>
 
 #include "umma_gemm.cuh"
@@ -33,6 +34,13 @@ int gemm_tc_launch(const rb200_gemm_desc* d, const Epilogue& epi, int group, int
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
+#ifdef RB200_ABLATE
+    {
+      const char* ab = getenv("RB200_GEMV_ABLATE");
+      p.ablate = ab ? atoi(ab) : 0;
+      p.partial = sc->partials;
+    }
+#endif
     const int rc = umma_gemm_run(p, d->weight_bits, zmode, sc->sm_count, stream);
     if (rc <= 0) return rc;
   }

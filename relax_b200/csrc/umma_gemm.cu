@@ -13,6 +13,7 @@ int umma_gemm_run(const GemvParams& p_in, int bits, int zmode, int sm_count, cud
   // coverage: whole 128-row tiles, whole 64-k blocks, TMA-loadable x
   if (p_in.n % kTileRows != 0 || p_in.k % kKBlock != 0) return 1;
   if ((reinterpret_cast<uintptr_t>(p_in.x) & 15u) != 0 || (p_in.ldx * 2) % 16 != 0) return 1;
+  if ((reinterpret_cast<uintptr_t>(p_in.out) & 15u) != 0 || (p_in.ldo * 2) % 16 != 0) return 1;  // 16-byte row stores
   static const bool disabled = getenv("RB200_GEMM_NO_TCGEN05") != nullptr;
   if (disabled) return 1;
 

@@ -52,6 +52,7 @@ constexpr int kNumA = 4;                    // TMEM A buffers of 32 columns (one
 constexpr int kTmemCols = 512;
 constexpr int kDCols = 256;                 // accumulator: columns [0, 256); A buffers follow
 constexpr int kMaxNb = 256;
+constexpr int kEpiStageBytes = 2 * 2 * 16 * kTileRows * 2;  // per group: two 16 x 128 fp16 buffers
 
 struct Params {
   GemvParams g;
@@ -62,8 +63,8 @@ struct Params {
 };
 
 inline size_t smem_bytes(int nb, int x_stages) {
-  return 1024 + (size_t)x_stages * nb * 128 + (size_t)kWStages * kWStageBytes +
-         (size_t)(2 * kWStages + 2 * kMaxXStages + 2 * kNumA + 2) * 8 + 16;
+  return 1024 + (size_t)x_stages * nb * 128 + (size_t)kWStages * kWStageBytes + kEpiStageBytes +
+         (size_t)(2 * kWStages + 2 * kMaxXStages + 2 * kNumA + 4) * 8 + 16;
 }
 
 #ifdef __CUDACC__
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int x_stage_bytes = nb * 128;
   uint8_t* x_ring = smem;
   uint8_t* w_ring = smem + (size_t)x_stages * x_stage_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(w_ring + (size_t)kWStages * kWStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(w_ring + (size_t)kWStages * kWStageBytes + kEpiStageBytes);
   uint64_t* w_full = bars;
   uint64_t* w_empty = w_full + kWStages;
   uint64_t* x_full = w_empty + kWStages;
@@ -160,7 +161,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* a_empty = a_full + kNumA;
   uint64_t* d_full = a_empty + kNumA;
   uint64_t* d_empty = d_full + 1;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(d_empty + 1);
+  uint64_t* e_bar = d_empty + 1;  // one per decode group: epilogue staging hand-over
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(e_bar + 2);
+  __half* e_stage = reinterpret_cast<__half*>(w_ring + (size_t)kWStages * kWStageBytes);  // [2 groups][2][16][128]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -181,6 +184,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     mbar_init(d_full, 1);
     mbar_init(d_empty, kDecodeWarps);
+    mbar_init(&e_bar[0], 4);
+    mbar_init(&e_bar[1], 4);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -200,6 +205,21 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int n_tiles = p.n / kTileRows;
   const int total_tiles = n_tiles * pp.m_tiles;
   bool ok = true;
+#ifdef RB200_ABLATE
+  const int ablate = p.ablate;
+  unsigned long long* tl = (blockIdx.x == 0 && (ablate & 65536) && p.partial) ? reinterpret_cast<unsigned long long*>(p.partial) + (1 << 18) : nullptr;
+#define RB200_GTL(role, i)                                                         \
+  do {                                                                             \
+    if (tl && (i) < 64) {                                                          \
+      unsigned long long t_;                                                       \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                        \
+      tl[(role) * 64 + (i)] = t_;                                                  \
+    }                                                                              \
+  } while (0)
+#else
+  constexpr int ablate = 0;
+#define RB200_GTL(role, i) do {} while (0)
+#endif
 
   if (warp == 0) {
     // ============================================================ producer: packed weights
@@ -235,10 +255,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t q = 0;       // running 64-k block counter (selects the A buffer)
       uint32_t tile_i = 0;  // tiles done by this CTA
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
+        RB200_GTL(0, (int)tile_i);
         if (!mbar_wait_parked(d_empty, (tile_i & 1u) ^ 1u, p.status)) {
           ok = false;
           break;
         }
+        RB200_GTL(1, (int)tile_i);
         tc_fence_after();
         for (int kb = 0; kb < kb_total; ++kb, ++q) {
           if (!mbar_wait_parked(&x_full[xs], xph, p.status)) {
@@ -251,10 +273,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           tc_fence_after();
+          if (kb == 0) RB200_GTL(2, (int)tile_i);
           const uint32_t xbase = smem_u32(x_ring + (size_t)xs * x_stage_bytes);
           const uint32_t a_tmem = a_col0 + ab * 32;
 #pragma unroll
           for (int j = 0; j < 4; ++j)
+            if (!(ablate & 8))
             tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == 0 && j == 0) ? 0u : 1u);
           tc_commit(&a_empty[ab]);
           tc_commit(&x_empty[xs]);
@@ -264,6 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         if (ok) tc_commit(d_full);
+        RB200_GTL(3, (int)tile_i);
       }
     }
   } else if (warp == 2) {
@@ -325,7 +350,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = false;
           break;
         }
-        if (lane == 0) {
+        if (lane == 0 && (ablate & 1)) {
+          mbar_arrive(&x_full[xs]);
+        } else if (lane == 0) {
           mbar_arrive_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
           tma_load_2d(x_ring + (size_t)xs * x_stage_bytes, &tmap_x, kb * kKBlock, m0, &x_full[xs]);
         }
@@ -359,6 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t wph = 0;
     uint32_t q = 0;
     uint32_t tile_i = 0;
+    uint32_t estep = 0;  // epilogue staging steps done by this group
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
       const int n_tile = t / pp.m_tiles, m_tile = t % pp.m_tiles;
       const int64_t n_row = (int64_t)n_tile * kTileRows + row;
@@ -367,6 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         s_chan = h2_bcast(p.s[n_row * p.s_n]);
         if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row * p.s_n]);
       }
+      if (dw == 0 && lane == 0) RB200_GTL(4, (int)tile_i);
       for (int chunk = 0; chunk < chunks && ok; ++chunk) {
         if (!mbar_wait_parked(&w_full[ws], wph, p.status)) {
           ok = false;
@@ -402,7 +431,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           tc_fence_after();
           uint32_t regs[32];
-          if (hi) decode_any<BITS, ZMODE, GROUP, SRC, 1>(kbm, p, up, c, zc, zconst_h2, group, regs);
+          if (ablate & 2) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) regs[i] = 0x3c003c00u;
+          } else if (hi) decode_any<BITS, ZMODE, GROUP, SRC, 1>(kbm, p, up, c, zc, zconst_h2, group, regs);
           else decode_any<BITS, ZMODE, GROUP, SRC, 0>(kbm, p, up, c, zc, zconst_h2, group, regs);
           tc_st32(lane_taddr | (a_col0 + ab * 32), regs);
           tc_wait_st();
@@ -420,23 +452,49 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) break;
       // ---------------------------------------------------------- epilogue of this tile
+      if (dw == 0 && lane == 0) RB200_GTL(5, (int)tile_i);
       if (!mbar_wait_parked(d_full, tile_i & 1u, p.status)) {
         ok = false;
         break;
       }
+      if (dw == 0 && lane == 0) RB200_GTL(6, (int)tile_i);
       tc_fence_after();
       const int64_t m0 = (int64_t)m_tile * nb;
       const int c_begin = grp * (nb / 2), c_end = c_begin + nb / 2;
-      for (int c0 = c_begin; c0 < c_end; c0 += 16) {
-        if (m0 + c0 >= p.m) break;
+      const int gj = (dw & 3) * 32 + lane;  // thread index inside the group
+      for (int c0 = c_begin; c0 < c_end; c0 += 16, ++estep) {
+        if (m0 + c0 >= p.m || (ablate & 4)) break;
         float v[16];
+        const int es_ = (c0 - c_begin) / 16;
+        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5);
         tc_ld16(lane_taddr | (d_col0 + c0), v);
+        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 1);
+        // transpose through shared memory: 16 batch rows x 128 weight rows of fp16 (rounded once,
+        // after the epilogue), so that global stores are whole 256-byte row segments
+        __half* st = e_stage + ((grp * 2 + (estep & 1u)) * 16) * kTileRows;
+        apply_epilogue16(v, p.epi, m0 + c0, p.m, n_row);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int64_t m = m0 + c0 + i;
-          if (m < p.m) p.out[m * p.ldo + n_row] = __float2half_rn(apply_epilogue(v[i], p.epi, m, n_row));
+        for (int i = 0; i < 16; ++i) st[i * kTileRows + row] = __float2half_rn(v[i]);
+        __syncwarp();
+        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 2);
+        if (lane == 0) mbar_arrive(&e_bar[grp]);
+        if (!mbar_wait_parked(&e_bar[grp], estep & 1u, p.status)) {
+          ok = false;
+          break;
         }
+        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 3);
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          const int mi = pass * 8 + (gj >> 4), ch = gj & 15;
+          const int64_t m = m0 + c0 + mi;
+          if (m < p.m)
+            *reinterpret_cast<uint4*>(p.out + m * p.ldo + (int64_t)n_tile * kTileRows + ch * 8) =
+                *reinterpret_cast<const uint4*>(st + mi * kTileRows + ch * 8);
+        }
+        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 4);
       }
+      if (!ok) break;
+      if (dw == 0 && lane == 0) RB200_GTL(7, (int)tile_i);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(d_empty);
