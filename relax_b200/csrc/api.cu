@@ -312,13 +312,12 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
       const unsigned epoch = ++sc->epoch;
       // Which decode kernel: measured crossovers on B200.  Few 128-row tiles (n <= 4096): the
       // cluster kernel, whose split-k partials meet in distributed shared memory, beats the
-      // global slot + flag fix-up by about 3 us.  Otherwise the stream-k warp-MMA kernel; for
-      // 17..32 rows on large weights the tcgen05 kernel (one MMA covers the whole batch).
+      // global slot + flag fix-up by about 3 us.  Otherwise the stream-k warp-MMA kernel.  The
+      // tcgen05 decode kernel (RB200_GEMV_KERNEL=1) loses to both at every measured shape - one
+      // tcgen05.mma costs ~172 clocks whatever the batch - and is kept for comparison only.
       static const int forced = getenv("RB200_GEMV_KERNEL") ? atoi(getenv("RB200_GEMV_KERNEL")) : -1;
-      const long long wbytes = (long long)p.n * p.k * d->weight_bits / 8;
       int which = 0;
-      if (p.m > 16 && wbytes >= (40ll << 20)) which = 1;
-      else if (p.n <= 4096) which = 2;
+      if (p.n <= 4096) which = 2;
       if (forced >= 0) which = forced;
       if (which == 0)
         return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,

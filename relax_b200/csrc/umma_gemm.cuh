@@ -48,7 +48,10 @@ constexpr int kScaleBoxBytes = 2048;
 constexpr int kWStageBytes = kWBytes + 2 * kScaleBoxBytes;
 constexpr int kWStages = 3;
 constexpr int kMaxXStages = 8;
-constexpr int kNumA = 4;                    // TMEM A buffers of 32 columns (one 64-k block each)
+#ifndef RB200_UM_NUMA
+#define RB200_UM_NUMA 4
+#endif
+constexpr int kNumA = RB200_UM_NUMA;        // TMEM A buffers of 32 columns (one 64-k block each)
 constexpr int kTmemCols = 512;
 constexpr int kDCols = 256;                 // accumulator: columns [0, 256); A buffers follow
 constexpr int kMaxNb = 256;
@@ -68,6 +71,15 @@ inline size_t smem_bytes(int nb, int x_stages) {
 }
 
 #ifdef __CUDACC__
+
+// hand-offs on the critical path (A buffers, x stages)
+__device__ __forceinline__ bool um_wait(uint64_t* bar, uint32_t parity, int* status) {
+#ifdef RB200_UM_SPIN
+  return mbar_wait_bounded(bar, parity, status);
+#else
+  return mbar_wait_parked(bar, parity, status);
+#endif
+}
 
 using gc::tma_load_2d;
 using ug::cp_async16;
@@ -256,6 +268,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t tile_i = 0;  // tiles done by this CTA
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
         RB200_GTL(0, (int)tile_i);
+#ifdef RB200_ABLATE
+        if (tl && tile_i < 32) tl[9 * 64 + tile_i] = (unsigned long long)clock64();
+#endif
         if (!mbar_wait_parked(d_empty, (tile_i & 1u) ^ 1u, p.status)) {
           ok = false;
           break;
@@ -263,12 +278,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         RB200_GTL(1, (int)tile_i);
         tc_fence_after();
         for (int kb = 0; kb < kb_total; ++kb, ++q) {
-          if (!mbar_wait_parked(&x_full[xs], xph, p.status)) {
+          if (!um_wait(&x_full[xs], xph, p.status)) {
             ok = false;
             break;
           }
           const uint32_t ab = q % kNumA;
-          if (!mbar_wait_parked(&a_full[ab], (q / kNumA) & 1u, p.status)) {
+          if (!um_wait(&a_full[ab], (q / kNumA) & 1u, p.status)) {
             ok = false;
             break;
           }
@@ -425,7 +440,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int kbm = 0; kbm < nblk; ++kbm, ++q) {
           if ((int)(q & 1u) != grp) continue;
           const uint32_t ab = q % kNumA;
-          if (!mbar_wait_parked(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
+          if (!um_wait(&a_empty[ab], ((q / kNumA) & 1u) ^ 1u, p.status)) {
             ok = false;
             break;
           }
