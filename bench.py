@@ -196,6 +196,9 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # the all-reduced messages are at most 256 KiB: plain peer transfers, no NVLink multicast
+        # bindings to unwind at tear-down
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     gen = torch.Generator(device=dev)
@@ -446,9 +449,20 @@ def run_gpu(args):
             "max_rel_err_vs_oracle": max_rel_err,
             "prefill": prefill,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tear-down: the graphs hold captured collectives, and destroying the communicator while
+        # they are alive was seen to block for good after the result line had been printed.
+        # Release them first, and bound the tear-down: the measurement is complete at this point.
+        graphs.clear()
+        torch.cuda.synchronize()
+        import threading
+        threading.Timer(20.0, lambda: os._exit(0)).start()
+        try:
+            dist.destroy_process_group()
+        finally:
+            sys.stdout.flush()
+            os._exit(0)
 
 
 def main():
