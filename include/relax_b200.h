@@ -152,6 +152,40 @@ RB200_API int rb200_gemm_fp16_int_bias_act_residual(
 RB200_API int rb200_gemm_fp16_intx_noalloc(const rb200_gemm_desc* desc, void* stream);
 
 /*
+ * Grouped matmul (mixture of experts): rows [indptr[e-1], indptr[e]) of x (indptr[-1] = 0) are
+ * multiplied by expert e's weight,  out[r] = x[r] @ decode(W[e])^T,  fp32 accumulation, fp16 out.
+ * Replaces cutlass_group_gemm as called from tvm_cutlass_group_gemm_sm90
+ * (src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64; argument building in
+ * src/runtime/contrib/cutlass/group_gemm_runner.cuh:154-209): same x / indptr / out convention
+ * (indptr is a DEVICE int64 array of end offsets, read by the kernel - no host synchronisation).
+ * weight_bits 16: dense fp16 weights [num_experts, n, k] (the reference's form).
+ * weight_bits 4 / 8: packed weights, one rb200_preprocess_weight result per expert
+ * (num_experts * n * k * bits / 8 bytes), scales / zeros addressed
+ *   e * scale_stride_e + n_idx * scale_stride_n + (k_idx / group_size) * scale_stride_g
+ * - an extension: the reference has no quantised grouped GEMM.
+ * Needs n % 128 == 0, k % 64 == 0, 16-byte aligned x / out rows, num_experts <= 64.
+ * workspace is accepted for signature parity and not used (nothing is allocated per call).
+ */
+typedef struct rb200_group_gemm_desc {
+  uint32_t struct_size;   /* sizeof(rb200_group_gemm_desc) */
+  int32_t weight_bits;    /* 4, 8 or 16 */
+  const void* x;          /* fp16 [total_rows, k], rows sorted by expert */
+  const void* w;
+  const void* scales;     /* fp16; NULL for 16-bit weights */
+  const void* zeros;      /* fp16 or NULL */
+  const int64_t* indptr;  /* device int64 [num_experts]: end row of each expert */
+  void* out;              /* fp16 [total_rows, n] */
+  int64_t total_rows, n, k, num_experts;
+  int64_t group_size;     /* <= 0 or >= k: one scale per output channel */
+  int64_t scale_stride_n, scale_stride_g, scale_stride_e;
+  float zero_const;       /* used when zeros == NULL (FT int4: 8, FT int8: 128, q4f16_1: 7) */
+  int32_t reserved;
+  void* workspace;
+  size_t workspace_bytes;
+} rb200_group_gemm_desc;
+RB200_API int rb200_group_gemm(const rb200_group_gemm_desc* desc, void* stream);
+
+/*
  * Debug/verification entry: writes the dequantised weight wq fp16 [n, k] (row-major) that the
  * matmul kernels feed to the tensor cores, produced by the same device decode routine.  Uses
  * the w / scales / zeros / group / stride / zero_const fields of the descriptor.  The arithmetic

@@ -32,6 +32,22 @@ class GemmDesc(ctypes.Structure):
     ]
 
 
+class GroupGemmDesc(ctypes.Structure):
+    """``rb200_group_gemm_desc`` of include/relax_b200.h."""
+
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32), ("weight_bits", ctypes.c_int32),
+        ("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+        ("zeros", ctypes.c_void_p), ("indptr", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("total_rows", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64),
+        ("num_experts", ctypes.c_int64), ("group_size", ctypes.c_int64),
+        ("scale_stride_n", ctypes.c_int64), ("scale_stride_g", ctypes.c_int64),
+        ("scale_stride_e", ctypes.c_int64),
+        ("zero_const", ctypes.c_float), ("reserved", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
 class DLDevice(ctypes.Structure):
     _fields_ = [("device_type", ctypes.c_int32), ("device_id", ctypes.c_int32)]
 
@@ -76,6 +92,7 @@ SIGNATURES = {
     "rb200_gemm_fp16_int_bias_act_residual": (_I, [_V, _V, _V, _V, _V, _V, _S, _S, _S, _I, _I, _I,
                                                    _I, _I, _V, ctypes.c_size_t, _V]),
     "rb200_dequantize": (_I, [ctypes.POINTER(GemmDesc), _V, _V]),
+    "rb200_group_gemm": (_I, [ctypes.POINTER(GroupGemmDesc), _V]),
     "RB200FuncGetGlobal": (_I, [_S, ctypes.POINTER(_V)]),
     "RB200FuncCall": (_I, [_V, ctypes.POINTER(Value), ctypes.POINTER(_I), _I,
                            ctypes.POINTER(Value), ctypes.POINTER(_I)]),

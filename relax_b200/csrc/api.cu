@@ -9,6 +9,7 @@
 #include "gemv.h"
 #include "gemv_cluster.cuh"
 #include "umma_gemv.cuh"
+#include "umma_gemm.cuh"
 #include "gemv_sk.cuh"
 #include "gemm_tc.h"
 #include "preprocess.h"
@@ -443,6 +444,48 @@ int rb200_gemm_fp16_int_bias_act_residual(const void* A, const void* B, const vo
   RB200_CHECK(residual != nullptr, "residual must be non-NULL");
   if (d.binary_op == RB200_BIN_NONE) d.binary_op = RB200_BIN_PLUS;
   return rb200_gemm_fp16_intx(&d, stream);
+}
+
+int rb200_group_gemm(const rb200_group_gemm_desc* d, void* stream_v) {
+  RB200_CHECK(d != nullptr, "descriptor is NULL");
+  RB200_CHECK(d->struct_size == sizeof(rb200_group_gemm_desc), "descriptor struct_size %u != %zu", d->struct_size,
+              sizeof(rb200_group_gemm_desc));
+  RB200_CHECK(d->weight_bits == 4 || d->weight_bits == 8 || d->weight_bits == 16,
+              "weight_bits must be 4, 8 or 16, got %d", d->weight_bits);
+  RB200_CHECK(d->num_experts >= 1, "num_experts must be >= 1");
+  RB200_CHECK(d->n > 0 && d->k > 0 && d->n < (1ll << 31) && d->k < (1ll << 31), "bad n=%lld / k=%lld",
+              (long long)d->n, (long long)d->k);
+  RB200_CHECK(d->total_rows >= 0 && d->total_rows < (1ll << 31), "bad total_rows=%lld", (long long)d->total_rows);
+  if (d->total_rows == 0) return 0;
+  RB200_CHECK(d->x && d->w && d->indptr && d->out, "x, w, indptr and out must be non-NULL");
+  RB200_CHECK(aligned16(d->w), "weight pointer must be 16-byte aligned");
+  const bool packed = d->weight_bits != 16;
+  RB200_CHECK(!packed || d->scales, "packed weights need scales");
+  DeviceScratch* sc = device_scratch(0, 0);
+  if (!sc) return -1;
+  GemvParams p;
+  memset(&p, 0, sizeof(p));
+  p.status = sc->status;
+  p.x = static_cast<const __half*>(d->x);
+  p.ldx = d->k;
+  p.w = static_cast<const uint8_t*>(d->w);
+  p.s = static_cast<const __half*>(d->scales);
+  p.z = static_cast<const __half*>(d->zeros);
+  p.s_n = packed ? d->scale_stride_n : 1;
+  p.s_g = d->scale_stride_g;
+  p.out = static_cast<__half*>(d->out);
+  p.ldo = d->n;
+  memset(&p.epi, 0, sizeof(p.epi));
+  p.m = (int)d->total_rows;
+  p.n = (int)d->n;
+  p.k = (int)d->k;
+  p.group = (d->group_size <= 0 || d->group_size >= d->k) ? 0 : (int)d->group_size;
+  p.zero_const = d->zero_const;
+  const bool int_zero = d->zero_const >= 0.0f && d->zero_const <= 255.0f && d->zero_const == (float)(int)d->zero_const;
+  const int zmode = (packed && (d->zeros || !int_zero)) ? kZeroGeneral : kZeroConstInt;
+  const int64_t w_expert_bytes = d->n * d->k * d->weight_bits / 8;
+  return umma_group_gemm_run(p, d->weight_bits, zmode, sc->sm_count, d->indptr, (int)d->num_experts, w_expert_bytes,
+                             packed ? d->scale_stride_e : 0, static_cast<cudaStream_t>(stream_v));
 }
 
 int rb200_dequantize(const rb200_gemm_desc* d, void* wq_out, void* stream_v) {

@@ -357,6 +357,125 @@ int pf_gemm_q4f16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, 
 }
 
 // (w_pre, scales, zeros|null, layout, weight_bits, group_size, zero_const, out fp16 [N, K])
+// ------------------------------------------------------------------ grouped GEMM
+// cutlass.group_gemm_fp16_sm90(x [M,K] f16, weight [E,N,K] f16, indptr [E] i64, workspace [..] u8, out [M,N] f16):
+// the argument list of tvm_cutlass_group_gemm_sm90 (src/runtime/contrib/cutlass/fp16_group_gemm.cu:41-62).
+int pf_group_gemm_fp16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
+  const char* fname = "cutlass.group_gemm_fp16_sm90";
+  Args a{v, tc, n_args, fname};
+  PF_CHECK(n_args == 5, "%s expects 5 arguments, got %d", fname, n_args);
+  const DLTensor *x, *w, *indptr, *ws, *out;
+  if (a.tensor(0, &x) || a.tensor(1, &w) || a.tensor(2, &indptr) || a.tensor(3, &ws, true) || a.tensor(4, &out))
+    return -1;
+  PF_CHECK(x->ndim == 2 && w->ndim == 3 && indptr->ndim == 1 && out->ndim == 2,
+           "%s: expected x 2-D, weight 3-D, indptr 1-D, out 2-D", fname);
+  if (check_tensor(fname, "x", x, kDLFloat, 16) || check_tensor(fname, "weight", w, kDLFloat, 16) ||
+      check_tensor(fname, "indptr", indptr, kDLInt, 64) || check_tensor(fname, "out", out, kDLFloat, 16))
+    return -1;
+  const int64_t E = w->shape[0], n = w->shape[1], k = w->shape[2];
+  PF_CHECK(indptr->shape[0] == E, "%s: indptr has %lld entries for %lld groups", fname,
+           (long long)indptr->shape[0], (long long)E);
+  PF_CHECK(x->shape[1] == k && out->shape[0] == x->shape[0] && out->shape[1] == n,
+           "%s: x / out shapes do not match weight [E, n, k]", fname);
+  rb200_group_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.struct_size = sizeof(d);
+  d.weight_bits = 16;
+  d.x = data_of(x);
+  d.w = data_of(w);
+  d.indptr = static_cast<const int64_t*>(data_of(indptr));
+  d.out = data_of(out);
+  d.total_rows = x->shape[0];
+  d.n = n;
+  d.k = k;
+  d.num_experts = E;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_group_gemm(&d, rb200_get_stream());
+}
+
+// Quantised experts.  layout 0 (cutlass.moe_gemm): FT form, w_pre int8 [E, K, N/2] (int4) or
+// [E, K, N] (int8) as written by cutlass.ft_preprocess_weight, scales [E, K/g, N] or [E, N].
+// layout 1 (relax_b200.moe_gemm_q4f16): w_pre [E, N, K/8] 32-bit words, scales [E, N, K/g].
+int moe_gemm(const char* fname, int layout, const DLTensor* x, const DLTensor* w, const DLTensor* s,
+             const DLTensor* z, const DLTensor* indptr, const DLTensor* out, int64_t group, double zero_const) {
+  PF_CHECK(x->ndim == 2 && w->ndim == 3 && indptr->ndim == 1 && out->ndim == 2,
+           "%s: expected x 2-D, weight 3-D, indptr 1-D, out 2-D", fname);
+  if (check_tensor(fname, "x", x, kDLFloat, 16) || check_tensor(fname, "scales", s, kDLFloat, 16) ||
+      check_tensor(fname, "indptr", indptr, kDLInt, 64) || check_tensor(fname, "out", out, kDLFloat, 16))
+    return -1;
+  if (z && check_tensor(fname, "zeros", z, kDLFloat, 16)) return -1;
+  PF_CHECK(compact(w) && w->device.device_type == kDLCUDA, "%s: weight must be a compact CUDA tensor", fname);
+  const int64_t E = w->shape[0], k = x->shape[1], n = out->shape[1];
+  rb200_group_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.struct_size = sizeof(d);
+  if (layout == 0) {
+    PF_CHECK(w->dtype.bits == 8 && w->shape[1] == k && (w->shape[2] == n || w->shape[2] * 2 == n),
+             "%s: weight must be int8 [E, k, n/2] or [E, k, n]", fname);
+    d.weight_bits = w->shape[2] == n ? 8 : 4;
+    const int64_t per_e = numel(s) / E;
+    PF_CHECK(numel(s) % E == 0 && per_e % n == 0 && per_e >= n, "%s: scales must be [E, k/g, n] or [E, n]", fname);
+    const int64_t kg = per_e / n;
+    d.group_size = kg == 1 ? -1 : k / kg;
+    PF_CHECK(kg == 1 || (k % kg == 0), "%s: scale rows do not divide k", fname);
+    d.scale_stride_n = 1;
+    d.scale_stride_g = n;
+    d.scale_stride_e = per_e;
+    d.zero_const = d.weight_bits == 4 ? 8.0f : 128.0f;
+  } else {
+    PF_CHECK(w->dtype.bits == 32 && w->shape[1] == n && w->shape[2] * 8 == k,
+             "%s: weight must be 32-bit words [E, n, k/8]", fname);
+    PF_CHECK(group > 0 && k % group == 0, "%s: group_size must divide k", fname);
+    d.weight_bits = 4;
+    const int64_t kg = k / group;
+    PF_CHECK(numel(s) == E * n * kg, "%s: scales must be [E, n, k/group_size]", fname);
+    d.group_size = group;
+    d.scale_stride_n = kg;
+    d.scale_stride_g = 1;
+    d.scale_stride_e = n * kg;
+    d.zero_const = (float)zero_const;
+  }
+  PF_CHECK(!z || numel(z) == numel(s), "%s: zeros must have the shape of scales", fname);
+  PF_CHECK(indptr->shape[0] == E && out->shape[0] == x->shape[0], "%s: indptr / out do not match x and weight", fname);
+  d.x = data_of(x);
+  d.w = data_of(w);
+  d.scales = data_of(s);
+  d.zeros = z ? data_of(z) : nullptr;
+  d.indptr = static_cast<const int64_t*>(data_of(indptr));
+  d.out = data_of(out);
+  d.total_rows = x->shape[0];
+  d.n = n;
+  d.k = k;
+  d.num_experts = E;
+  return rb200_group_gemm(&d, rb200_get_stream());
+}
+// (x, w_pre, scales, zeros|null, indptr, workspace|null, out)
+int pf_moe_gemm(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
+  const char* fname = "cutlass.moe_gemm";
+  Args a{v, tc, n_args, fname};
+  PF_CHECK(n_args == 7, "%s expects 7 arguments, got %d", fname, n_args);
+  const DLTensor *x, *w, *s, *z, *indptr, *ws, *out;
+  if (a.tensor(0, &x) || a.tensor(1, &w) || a.tensor(2, &s) || a.tensor(3, &z, true) || a.tensor(4, &indptr) ||
+      a.tensor(5, &ws, true) || a.tensor(6, &out))
+    return -1;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return moe_gemm(fname, 0, x, w, s, z, indptr, out, 0, 0.0);
+}
+// (x, w_pre, scales, zeros|null, indptr, group_size, zero_const, out)
+int pf_moe_gemm_q4f16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
+  const char* fname = "relax_b200.moe_gemm_q4f16";
+  Args a{v, tc, n_args, fname};
+  PF_CHECK(n_args == 8, "%s expects 8 arguments, got %d", fname, n_args);
+  const DLTensor *x, *w, *s, *z, *indptr, *out;
+  int64_t group;
+  double zc;
+  if (a.tensor(0, &x) || a.tensor(1, &w) || a.tensor(2, &s) || a.tensor(3, &z, true) || a.tensor(4, &indptr) ||
+      a.integer(5, &group) || a.real(6, &zc) || a.tensor(7, &out))
+    return -1;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return moe_gemm(fname, 1, x, w, s, z, indptr, out, group, zc);
+}
+
 int pf_dequantize(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
   const char* fname = "relax_b200.dequantize";
   Args a{v, tc, n_args, fname};
@@ -426,6 +545,9 @@ void ensure_builtins() {
   register_builtin("cutlass.ft_gemm_fp16_int8", pf_ft_gemm_int8);
   register_builtin("relax_b200.gemm_fp16_q4f16", pf_gemm_q4f16);
   register_builtin("relax_b200.dequantize", pf_dequantize);
+  register_builtin("cutlass.group_gemm_fp16_sm90", pf_group_gemm_fp16);
+  register_builtin("cutlass.moe_gemm", pf_moe_gemm);
+  register_builtin("relax_b200.moe_gemm_q4f16", pf_moe_gemm_q4f16);
   register_builtin("runtime.get_cuda_stream", pf_get_stream);
   register_builtin("runtime.set_cuda_stream", pf_set_stream);
 }

@@ -8,47 +8,73 @@
 
 namespace rb200 {
 
-int umma_gemm_run(const GemvParams& p_in, int bits, int zmode, int sm_count, cudaStream_t stream) {
+static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count, const int64_t* indptr,
+                      int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, bool grouped,
+                      cudaStream_t stream) {
   using namespace um;
-  // coverage: whole 128-row tiles, whole 64-k blocks, TMA-loadable x
-  if (p_in.n % kTileRows != 0 || p_in.k % kKBlock != 0) return 1;
-  if ((reinterpret_cast<uintptr_t>(p_in.x) & 15u) != 0 || (p_in.ldx * 2) % 16 != 0) return 1;
-  if ((reinterpret_cast<uintptr_t>(p_in.out) & 15u) != 0 || (p_in.ldo * 2) % 16 != 0) return 1;  // 16-byte row stores
+  // coverage: whole 128-row tiles, whole 64-k blocks, TMA-loadable x, 16-byte row stores
+  const bool covered = p_in.n % kTileRows == 0 && p_in.k % kKBlock == 0 &&
+                       (reinterpret_cast<uintptr_t>(p_in.x) & 15u) == 0 && (p_in.ldx * 2) % 16 == 0 &&
+                       (reinterpret_cast<uintptr_t>(p_in.out) & 15u) == 0 && (p_in.ldo * 2) % 16 == 0;
+  if (!covered) {
+    RB200_CHECK(!grouped, "grouped GEMM needs n %% 128 == 0, k %% 64 == 0 and 16-byte aligned x / out rows "
+                "(n=%d, k=%d)", p_in.n, p_in.k);
+    return 1;
+  }
   static const bool disabled = getenv("RB200_GEMM_NO_TCGEN05") != nullptr;
-  if (disabled) return 1;
+  if (disabled && !grouped) return 1;
+  RB200_CHECK(num_experts >= 1 && num_experts <= kMaxExperts, "num_experts=%d outside [1, %d]", num_experts,
+              kMaxExperts);
 
   Params pp;
   memset(&pp, 0, sizeof(pp));
   pp.g = p_in;
   GemvParams& p = pp.g;
-  // balanced batch tiles of at most 256 rows, padded to the 32 rows the epilogue split needs
-  pp.m_tiles = (p.m + kMaxNb - 1) / kMaxNb;
-  pp.nb = (((p.m + pp.m_tiles - 1) / pp.m_tiles) + 31) / 32 * 32;
+  pp.indptr = indptr;
+  pp.num_experts = num_experts;
+  pp.w_expert_bytes = w_expert_bytes;
+  pp.s_expert_stride = s_expert_stride;
+  if (grouped) {
+    // the split of the rows is known only on the device: tiles as wide as the MMA allows, since
+    // one tcgen05.mma costs the same for 32 batch rows as for 256
+    pp.nb = p.m >= kMaxNb ? kMaxNb : (p.m + 31) / 32 * 32;
+  } else {
+    // balanced batch tiles of at most 256 rows, padded to the 32 rows the epilogue split needs
+    const int m_tiles = (p.m + kMaxNb - 1) / kMaxNb;
+    pp.nb = (((p.m + m_tiles - 1) / m_tiles) + 31) / 32 * 32;
+  }
 
   Launch l;
   l.zmode = zmode;
-  if (p.group <= 0 || p.group >= p.k) {
-    l.group_code = 0;
-  } else {
-    RB200_CHECK(p.group % 16 == 0 && p.k % p.group == 0,
-                "group_size=%d must divide k=%d and be a multiple of 16", p.group, p.k);
-    l.group_code = (bits == 4 && (p.group == 32 || p.group == 64 || p.group == 128)) ? p.group : -1;
-  }
   l.src = ug::kSrcGlobal;
-  const int64_t kg = l.group_code != 0 ? p.k / p.group : 0;
-  const bool al = (reinterpret_cast<uintptr_t>(p.s) & 15u) == 0 &&
-                  (p.z == nullptr || (reinterpret_cast<uintptr_t>(p.z) & 15u) == 0);
-  if (bits == 4 && l.group_code > 0 && al) {
-    if (p.s_g == 1 && p.s_n == kg && p.group == 32 && (kg * 2) % 16 == 0) l.src = ug::kSrcSmemNK;
-    else if (p.s_n == 1 && p.s_g == p.n && (p.n * 2) % 16 == 0) l.src = ug::kSrcSmemKN;
+  l.group_code = 0;
+  if (bits != 16) {
+    if (p.group <= 0 || p.group >= p.k) {
+      l.group_code = 0;
+    } else {
+      RB200_CHECK(p.group % 16 == 0 && p.k % p.group == 0,
+                  "group_size=%d must divide k=%d and be a multiple of 16", p.group, p.k);
+      l.group_code = (bits == 4 && (p.group == 32 || p.group == 64 || p.group == 128)) ? p.group : -1;
+    }
+    const int64_t kg = l.group_code != 0 ? p.k / p.group : 0;
+    const bool al = (reinterpret_cast<uintptr_t>(p.s) & 15u) == 0 &&
+                    (p.z == nullptr || (reinterpret_cast<uintptr_t>(p.z) & 15u) == 0) &&
+                    (s_expert_stride * 2) % 16 == 0;
+    if (bits == 4 && l.group_code > 0 && al) {
+      if (p.s_g == 1 && p.s_n == kg && p.group == 32 && (kg * 2) % 16 == 0) l.src = ug::kSrcSmemNK;
+      else if (p.s_n == 1 && p.s_g == p.n && (p.n * 2) % 16 == 0) l.src = ug::kSrcSmemKN;
+    }
+    if (l.src != ug::kSrcGlobal && zmode == kZeroGeneral && p.z) pp.has_z_tile = 1;
+    RB200_CHECK(p.s_n != 0 && s_expert_stride % p.s_n == 0, "expert stride of the scales must be a multiple of their row stride");
   }
-  if (l.src != ug::kSrcGlobal && zmode == kZeroGeneral && p.z) pp.has_z_tile = 1;
 
-  const long long total_tiles = (long long)(p.n / kTileRows) * pp.m_tiles;
   static const int env_grid = getenv("RB200_GEMM_GRID") ? atoi(getenv("RB200_GEMM_GRID")) : 0;
   long long grid = sm_count;  // one persistent CTA per SM (a tensor-memory kernel gets occupancy 1)
   if (env_grid > 0) grid = env_grid;
-  if (grid > total_tiles) grid = total_tiles;
+  if (!grouped) {
+    const long long total_tiles = (long long)(p.n / kTileRows) * ((p.m + pp.nb - 1) / pp.nb);
+    if (grid > total_tiles) grid = total_tiles;
+  }
   l.grid = (int)grid;
 
   const size_t budget = (size_t)227 * 1024;
@@ -65,11 +91,30 @@ int umma_gemm_run(const GemvParams& p_in, int bits, int zmode, int sm_count, cud
                          CU_TENSOR_MAP_SWIZZLE_128B) != 0)
     return -1;
 
+  if (bits == 16) {
+    CUtensorMap tw;
+    const unsigned long long dims[3] = {(unsigned long long)p.k, (unsigned long long)p.n, (unsigned long long)num_experts};
+    const unsigned long long strides[2] = {(unsigned long long)p.k * 2, (unsigned long long)w_expert_bytes};
+    const unsigned box[3] = {kKBlock, kTileRows, 1};
+    if (make_tensor_map(&tw, p.w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+      return -1;
+    return launch_gemm_f16(pp, l, tx, tw, stream);
+  }
   if (bits == 4) {
     if (zmode == kZeroConstInt) return launch_gemm_i4c(pp, l, tx, stream);
     return launch_gemm_i4g(pp, l, tx, stream);
   }
   return launch_gemm_i8(pp, l, tx, stream);
+}
+
+int umma_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, cudaStream_t stream) {
+  return run_common(p, bits, zmode, sm_count, nullptr, 1, 0, 0, false, stream);
+}
+
+int umma_group_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, const int64_t* indptr,
+                        int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, cudaStream_t stream) {
+  RB200_CHECK(indptr != nullptr, "indptr must be non-NULL");
+  return run_common(p, bits, zmode, sm_count, indptr, num_experts, w_expert_bytes, s_expert_stride, true, stream);
 }
 
 }  // namespace rb200

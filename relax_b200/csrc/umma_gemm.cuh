@@ -57,17 +57,24 @@ constexpr int kDCols = 256;                 // accumulator: columns [0, 256); A 
 constexpr int kMaxNb = 256;
 constexpr int kEpiStageBytes = 2 * 2 * 16 * kTileRows * 2;  // per group: two 16 x 128 fp16 buffers
 
+constexpr int kMaxExperts = 64;
+
 struct Params {
   GemvParams g;
   int nb;          // batch rows per tile = MMA N (multiple of 32, <= 256)
-  int m_tiles;
   int x_stages;
   int has_z_tile;
+  // grouped form: rows [indptr[e-1], indptr[e]) of x / out belong to expert e (indptr: device,
+  // end offsets); indptr == nullptr: one group holding all g.m rows
+  const int64_t* indptr;
+  int num_experts;
+  int64_t w_expert_bytes;   // bytes between experts' packed weights
+  int64_t s_expert_stride;  // elements between experts' scale (and zero) tensors
 };
 
 inline size_t smem_bytes(int nb, int x_stages) {
   return 1024 + (size_t)x_stages * nb * 128 + (size_t)kWStages * kWStageBytes + kEpiStageBytes +
-         (size_t)(2 * kWStages + 2 * kMaxXStages + 2 * kNumA + 4) * 8 + 16;
+         (size_t)(2 * kWStages + 2 * kMaxXStages + 2 * kNumA + 4) * 8 + 16 + (3 * kMaxExperts + 4) * sizeof(int);
 }
 
 #ifdef __CUDACC__
@@ -138,6 +145,50 @@ __device__ __forceinline__ void decode_block8(const GemvParams& p, const RowCtx&
   }
 }
 
+// D[tmem] (+)= A[smem desc] * B[smem desc]; kind::f16, fp32 accumulate
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Work item: one (expert, 128-row weight tile, batch tile).  Items are numbered expert by expert,
+// batch tiles fastest; the tables live in shared memory (built once per CTA from indptr).
+struct Tile {
+  int e, n_tile;
+  int m0, m_end;  // first batch row of the tile, end of the expert's rows
+};
+struct TileTables {
+  int base[kMaxExperts + 1];
+  int row_begin[kMaxExperts];
+  int row_end[kMaxExperts];
+};
+__device__ __forceinline__ Tile get_tile(const TileTables& tt, int num_experts, int nb, int t) {
+  int e = 0;
+  while (e + 1 < num_experts && t >= tt.base[e + 1]) ++e;
+  const int local = t - tt.base[e];
+  const int rows = tt.row_end[e] - tt.row_begin[e];
+  const int mt = (rows + nb - 1) / nb;
+  Tile tl;
+  tl.e = e;
+  tl.n_tile = local / mt;
+  tl.m0 = tt.row_begin[e] + (local % mt) * nb;
+  tl.m_end = tt.row_end[e];
+  return tl;
+}
+
 template <int BITS, int ZMODE, int GROUP, int SRC, int HI>
 __device__ __forceinline__ void decode_any(int kbm, const GemvParams& p, const ug::Params& up, const RowCtx& c,
                                            const ZeroConsts& zc, uint32_t zconst_h2, int group,
@@ -152,10 +203,15 @@ __device__ __forceinline__ void decode_any(int kbm, const GemvParams& p, const u
 
 template <int BITS, int ZMODE, int GROUP, int SRC>
 __global__ void __launch_bounds__(kThreads, 1)
-    umma_gemm_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_x) {
-  constexpr int kTilesPerBlock = BITS == 4 ? 1 : 2;       // fragment tiles per 64-k MMA block
-  constexpr int kBlocksPerChunk = 4 / kTilesPerBlock;     // MMA blocks per weight stage
-  constexpr int kFragK = BITS == 4 ? 64 : 32;
+    umma_gemm_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_x,
+                     const __grid_constant__ CUtensorMap tmap_w) {
+  // BITS == 16: dense fp16 weights [E, N, K]; a weight stage is one 128 x 64 tile loaded by TMA
+  // in the tensor core's swizzled K-major layout and the MMA takes both operands from shared
+  // memory; the decode warps only run the epilogue.
+  constexpr bool kDense = BITS == 16;
+  constexpr int kTilesPerBlock = BITS == 8 ? 2 : 1;       // fragment tiles per 64-k MMA block
+  constexpr int kBlocksPerChunk = kDense ? 1 : 4 / kTilesPerBlock;  // MMA blocks per weight stage
+  constexpr int kFragK = BITS == 8 ? 32 : 64;
   extern __shared__ uint8_t smem_raw[];
   const GemvParams& p = pp.g;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -175,6 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* d_empty = d_full + 1;
   uint64_t* e_bar = d_empty + 1;  // one per decode group: epilogue staging hand-over
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(e_bar + 2);
+  TileTables& tt = *reinterpret_cast<TileTables*>(tmem_holder + 4);
   __half* e_stage = reinterpret_cast<__half*>(w_ring + (size_t)kWStages * kWStageBytes);  // [2 groups][2][16][128]
 
   const int tid = threadIdx.x;
@@ -184,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (tid == 0) {
     for (int s = 0; s < kWStages; ++s) {
       mbar_init(&w_full[s], 1 + (SRC != kSrcGlobal ? 32 : 0));  // expect_tx arrival (+ scale loader lanes)
-      mbar_init(&w_empty[s], kDecodeWarps);
+      mbar_init(&w_empty[s], kDense ? 1 : kDecodeWarps);
     }
     for (int s = 0; s < x_stages; ++s) {
       mbar_init(&x_full[s], 1);
@@ -204,7 +261,24 @@ __global__ void __launch_bounds__(kThreads, 1)
     tmem_alloc(tmem_holder, kTmemCols);
     tmem_relinquish();
   }
+  const int n_tiles = p.n / kTileRows;
+  if (tid < pp.num_experts) {
+    const int64_t r0 = pp.indptr ? (tid ? pp.indptr[tid - 1] : 0) : 0;
+    int64_t r1 = pp.indptr ? pp.indptr[tid] : p.m;
+    if (r1 > p.m) r1 = p.m;  // never past the rows x / out hold
+    tt.row_begin[tid] = (int)r0;
+    tt.row_end[tid] = r1 > r0 ? (int)r1 : (int)r0;
+  }
   tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0;
+    for (int e = 0; e < pp.num_experts; ++e) {
+      tt.base[e] = acc;
+      acc += n_tiles * ((tt.row_end[e] - tt.row_begin[e] + pp.nb - 1) / pp.nb);
+    }
+    tt.base[pp.num_experts] = acc;
+  }
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
@@ -213,9 +287,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int kb_total = p.k / kKBlock;             // MMA blocks along k
   const int ft_total = p.k / kFragK;              // fragment tiles along k
-  const int chunks = (ft_total + 3) / 4;          // weight stages per tile
-  const int n_tiles = p.n / kTileRows;
-  const int total_tiles = n_tiles * pp.m_tiles;
+  const int chunks = kDense ? kb_total : (ft_total + 3) / 4;  // weight stages per tile
+  const int total_tiles = tt.base[pp.num_experts];
+  const int ne = pp.num_experts;
   bool ok = true;
 #ifdef RB200_ABLATE
   const int ablate = p.ablate;
@@ -238,18 +312,25 @@ __global__ void __launch_bounds__(kThreads, 1)
     int ws = 0;
     uint32_t wph = 0;
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-      const int n_tile = t / pp.m_tiles;
+      const Tile tile = get_tile(tt, ne, nb, t);
+      const uint8_t* w_e = p.w + (int64_t)tile.e * pp.w_expert_bytes;
       for (int chunk = 0; chunk < chunks; ++chunk) {
         if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
           ok = false;
           break;
         }
         if (lane == 0) {
-          const int nft = min(4, ft_total - chunk * 4);
-          const uint32_t wbytes = (uint32_t)nft * 8 * 512;
-          mbar_arrive_expect_tx(&w_full[ws], wbytes);
-          bulk_g2s(w_ring + (size_t)ws * kWStageBytes, p.w + frag_stage_offset(n_tile, chunk, p.n / 16, ft_total),
-                   wbytes, &w_full[ws]);
+          if (kDense) {
+            mbar_arrive_expect_tx(&w_full[ws], (uint32_t)kWBytes);
+            tma_load_3d(w_ring + (size_t)ws * kWStageBytes, &tmap_w, chunk * kKBlock, tile.n_tile * kTileRows, tile.e,
+                        &w_full[ws]);
+          } else {
+            const int nft = min(4, ft_total - chunk * 4);
+            const uint32_t wbytes = (uint32_t)nft * 8 * 512;
+            mbar_arrive_expect_tx(&w_full[ws], wbytes);
+            bulk_g2s(w_ring + (size_t)ws * kWStageBytes, w_e + frag_stage_offset(tile.n_tile, chunk, p.n / 16, ft_total),
+                     wbytes, &w_full[ws]);
+          }
         }
         __syncwarp();
         if (++ws == kWStages) {
@@ -266,6 +347,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t xph = 0;
       uint32_t q = 0;       // running 64-k block counter (selects the A buffer)
       uint32_t tile_i = 0;  // tiles done by this CTA
+      int ws = 0;
+      uint32_t wph = 0;
+      (void)ws;
+      (void)wph;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
         RB200_GTL(0, (int)tile_i);
 #ifdef RB200_ABLATE
@@ -283,19 +368,37 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           const uint32_t ab = q % kNumA;
-          if (!um_wait(&a_full[ab], (q / kNumA) & 1u, p.status)) {
+          if (kDense) {
+            if (!um_wait(&w_full[ws], wph, p.status)) {
+              ok = false;
+              break;
+            }
+          } else if (!um_wait(&a_full[ab], (q / kNumA) & 1u, p.status)) {
             ok = false;
             break;
           }
           tc_fence_after();
           if (kb == 0) RB200_GTL(2, (int)tile_i);
           const uint32_t xbase = smem_u32(x_ring + (size_t)xs * x_stage_bytes);
-          const uint32_t a_tmem = a_col0 + ab * 32;
+          if (kDense) {
+            const uint32_t wbase = smem_u32(w_ring + (size_t)ws * kWStageBytes);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (!(ablate & 8))
-            tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == 0 && j == 0) ? 0u : 1u);
-          tc_commit(&a_empty[ab]);
+            for (int j = 0; j < 4; ++j)
+              tc_mma_ss(d_col0, make_b_desc(wbase + j * 32), make_b_desc(xbase + j * 32), idesc,
+                        (kb == 0 && j == 0) ? 0u : 1u);
+            tc_commit(&w_empty[ws]);
+            if (++ws == kWStages) {
+              ws = 0;
+              wph ^= 1u;
+            }
+          } else {
+            const uint32_t a_tmem = a_col0 + ab * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (!(ablate & 8))
+                tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == 0 && j == 0) ? 0u : 1u);
+            tc_commit(&a_empty[ab]);
+          }
           tc_commit(&x_empty[xs]);
           if (++xs == x_stages) {
             xs = 0;
@@ -308,12 +411,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 2) {
     // ============================================================ scale / zero tiles of each chunk
-    if (SRC != kSrcGlobal) {
+    if (SRC != kSrcGlobal && !kDense) {
       int ws = 0;
       uint32_t wph = 0;
       const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const int64_t n0 = (int64_t)(t / pp.m_tiles) * kTileRows;
+        const Tile tile = get_tile(tt, ne, nb, t);
+        const int64_t n0 = (int64_t)tile.n_tile * kTileRows;
+        const __half* s_e = p.s + (int64_t)tile.e * pp.s_expert_stride;
+        const __half* z_e = p.z ? p.z + (int64_t)tile.e * pp.s_expert_stride : nullptr;
         for (int chunk = 0; chunk < chunks; ++chunk) {
           if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
             ok = false;
@@ -329,8 +435,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int i = 0; i < 4; ++i) {
               const int row = lane + 32 * i;
               const int64_t o = (n0 + row) * kg + (sv ? g0 : 0);
-              cp_async16(wsb + kWBytes + row * 16, p.s + o, sv);
-              if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(wsb + kWBytes + kScaleBoxBytes + row * 16, p.z + o, sv);
+              cp_async16(wsb + kWBytes + row * 16, s_e + o, sv);
+              if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(wsb + kWBytes + kScaleBoxBytes + row * 16, z_e + o, sv);
             }
           } else {
             // [groups of the chunk][128 rows]: 256 bytes per group row
@@ -340,9 +446,9 @@ __global__ void __launch_bounds__(kThreads, 1)
               const int64_t grow = (int64_t)chunk * kG + gl;
               const uint32_t sv = grow < kg ? 16u : 0u;
               const int64_t o = (sv ? grow : 0) * p.n + n0 + cc * 8;
-              cp_async16(wsb + kWBytes + gl * 256 + cc * 16, p.s + o, sv);
+              cp_async16(wsb + kWBytes + gl * 256 + cc * 16, s_e + o, sv);
               if (ZMODE == kZeroGeneral && pp.has_z_tile)
-                cp_async16(wsb + kWBytes + kScaleBoxBytes + gl * 256 + cc * 16, p.z + o, sv);
+                cp_async16(wsb + kWBytes + kScaleBoxBytes + gl * 256 + cc * 16, z_e + o, sv);
             }
           }
           cp_async_arrive(&w_full[ws]);
@@ -359,7 +465,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     int xs = 0;
     uint32_t xph = 0;
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-      const int m0 = (t % pp.m_tiles) * nb;
+      const int m0 = get_tile(tt, ne, nb, t).m0;
       for (int kb = 0; kb < kb_total; ++kb) {
         if (!mbar_wait_parked(&x_empty[xs], xph ^ 1u, p.status)) {
           ok = false;
@@ -386,7 +492,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int hi = w4 & 1;               // rows g (0) or g+8 (1) of the 16-row blocks
     const int bl = (w4 >> 1) * 4 + (lane >> 3);
     const int g = lane & 7;
-    const int row = 16 * bl + g + 8 * hi;
+    // weight row held by this thread's TMEM lane: the decode order for packed weights, the
+    // natural order when the A operand came from a TMA tile
+    const int row = kDense ? 32 * w4 + lane : 16 * bl + g + 8 * hi;
     const uint32_t lane_taddr = (uint32_t)(32 * w4) << 16;
     const ZeroConsts zc = make_zero_consts(ZMODE, p.zero_const);
     const uint32_t zconst_h2 = h2_bcast(__float2half_rn(p.zero_const));
@@ -403,15 +511,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t tile_i = 0;
     uint32_t estep = 0;  // epilogue staging steps done by this group
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
-      const int n_tile = t / pp.m_tiles, m_tile = t % pp.m_tiles;
+      const Tile tile = get_tile(tt, ne, nb, t);
+      const int n_tile = tile.n_tile;
       const int64_t n_row = (int64_t)n_tile * kTileRows + row;
+      // row index for scale / zero addressing: the expert's offset folded in (the host checks that
+      // the expert stride is a multiple of the row stride)
+      const int64_t n_row_s = kDense ? 0 : n_row + (int64_t)tile.e * (pp.s_expert_stride / (p.s_n ? p.s_n : 1));
       uint32_t s_chan = 0, z_chan = zconst_h2;
-      if (GROUP == 0) {
-        s_chan = h2_bcast(p.s[n_row * p.s_n]);
-        if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row * p.s_n]);
+      if (GROUP == 0 && !kDense) {
+        s_chan = h2_bcast(p.s[n_row_s * p.s_n]);
+        if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row_s * p.s_n]);
       }
       if (dw == 0 && lane == 0) RB200_GTL(4, (int)tile_i);
-      for (int chunk = 0; chunk < chunks && ok; ++chunk) {
+      for (int chunk = 0; chunk < (kDense ? 0 : chunks) && ok; ++chunk) {
         if (!mbar_wait_parked(&w_full[ws], wph, p.status)) {
           ok = false;
           break;
@@ -434,7 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         c.s_chan = s_chan;
         c.z_chan = z_chan;
         c.row = row;
-        c.n_row = n_row;
+        c.n_row = n_row_s;
         c.kb0 = chunk * kBlocksPerChunk;
 #pragma unroll 1
         for (int kbm = 0; kbm < nblk; ++kbm, ++q) {
@@ -474,11 +586,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (dw == 0 && lane == 0) RB200_GTL(6, (int)tile_i);
       tc_fence_after();
-      const int64_t m0 = (int64_t)m_tile * nb;
+      const int64_t m0 = tile.m0;
+      const int64_t m_end = tile.m_end;
       const int c_begin = grp * (nb / 2), c_end = c_begin + nb / 2;
       const int gj = (dw & 3) * 32 + lane;  // thread index inside the group
       for (int c0 = c_begin; c0 < c_end; c0 += 16, ++estep) {
-        if (m0 + c0 >= p.m || (ablate & 4)) break;
+        if (m0 + c0 >= m_end || (ablate & 4)) break;
         float v[16];
         const int es_ = (c0 - c_begin) / 16;
         if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5);
@@ -487,7 +600,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         // transpose through shared memory: 16 batch rows x 128 weight rows of fp16 (rounded once,
         // after the epilogue), so that global stores are whole 256-byte row segments
         __half* st = e_stage + ((grp * 2 + (estep & 1u)) * 16) * kTileRows;
-        apply_epilogue16(v, p.epi, m0 + c0, p.m, n_row);
+        apply_epilogue16(v, p.epi, m0 + c0, m_end, n_row);
 #pragma unroll
         for (int i = 0; i < 16; ++i) st[i * kTileRows + row] = __float2half_rn(v[i]);
         __syncwarp();
@@ -502,7 +615,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int pass = 0; pass < 2; ++pass) {
           const int mi = pass * 8 + (gj >> 4), ch = gj & 15;
           const int64_t m = m0 + c0 + mi;
-          if (m < p.m)
+          if (m < m_end)
             *reinterpret_cast<uint4*>(p.out + m * p.ldo + (int64_t)n_tile * kTileRows + ch * 8) =
                 *reinterpret_cast<const uint4*>(st + mi * kTileRows + ch * 8);
         }
@@ -535,11 +648,18 @@ struct Launch {
 int launch_gemm_i4c(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream);
 int launch_gemm_i4g(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream);
 int launch_gemm_i8(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream);
+int launch_gemm_f16(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& tw, cudaStream_t stream);
 
 }  // namespace um
 
 // Host entry: returns 1 when the problem is outside this kernel's coverage (the caller then runs
 // batch slices on the decode kernel), 0 on launch, -1 on error.
 int umma_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, cudaStream_t stream);
+
+// Grouped form (bits 4 / 8: packed weights per expert in the fragment layout; bits 16: dense fp16
+// [E, N, K]).  p.m = total rows of x / out; indptr = device int64[num_experts] of end offsets.
+// 0 on launch, -1 on error (shapes outside the kernel's coverage are errors here).
+int umma_group_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, const int64_t* indptr,
+                        int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, cudaStream_t stream);
 
 }  // namespace rb200

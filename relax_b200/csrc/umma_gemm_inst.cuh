@@ -6,7 +6,7 @@ namespace rb200 {
 namespace um {
 
 template <int BITS, int ZMODE, int GROUP, int SRC>
-int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream) {
+int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& tw, cudaStream_t stream) {
   auto kern = umma_gemm_kernel<BITS, ZMODE, GROUP, SRC>;
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -15,7 +15,7 @@ int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaSt
     RB200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured_device = dev;
   }
-  kern<<<l.grid, kThreads, l.smem, stream>>>(pp, tx);
+  kern<<<l.grid, kThreads, l.smem, stream>>>(pp, tx, tw);
   RB200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -23,7 +23,7 @@ int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaSt
 template <int BITS, int ZMODE>
 int launch_gs(const Params& pp, const Launch& l, const CUtensorMap& tx, cudaStream_t stream) {
 #define RB200_CASE(G, S) \
-  if (l.group_code == (G) && l.src == (S)) return launch_inst<BITS, ZMODE, G, S>(pp, l, tx, stream)
+  if (l.group_code == (G) && l.src == (S)) return launch_inst<BITS, ZMODE, G, S>(pp, l, tx, tx, stream)
   RB200_CASE(0, kSrcGlobal);
   RB200_CASE(-1, kSrcGlobal);
   if constexpr (BITS == 4) {

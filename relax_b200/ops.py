@@ -64,3 +64,35 @@ def dequantize(w_pre, scales, n: int, k: int, weight_bits: int, layout: int, zer
     get_global_func("relax_b200.dequantize")(w_pre, scales, zeros, int(layout), int(weight_bits),
                                              int(group_size), float(zero_const), out)
     return out
+
+
+def group_gemm_fp16(x, weight, indptr, workspace=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[r0:r1] = x[r0:r1] @ weight[g].T`` for every group g with ``r1 = indptr[g]``: the call
+    src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64 registers as
+    ``cutlass.group_gemm_fp16_sm90`` (x fp16 [M, K], weight fp16 [E, N, K], indptr int64 [E] on
+    the device)."""
+    if out is None:
+        out = torch.empty(x.shape[0], weight.shape[1], dtype=torch.float16, device=x.device)
+    get_global_func("cutlass.group_gemm_fp16_sm90")(x, weight, indptr, workspace, out)
+    return out
+
+
+def moe_gemm_ft(x, w_pre, scales, indptr, zeros=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Grouped decode-matmul over FT-layout experts: ``w_pre`` int8 [E, K, N/2] (int4) or
+    [E, K, N] (int8) from :func:`preprocess_weight_ft`, ``scales`` fp16 [E, K/g, N] or [E, N]."""
+    n = scales.shape[-1]
+    if out is None:
+        out = torch.empty(x.shape[0], n, dtype=torch.float16, device=x.device)
+    get_global_func("cutlass.moe_gemm")(x, w_pre, scales, zeros, indptr, None, out)
+    return out
+
+
+def moe_gemm_q4f16(x, w_pre, scales, indptr, zeros=None, group_size: int = 32, zero_const: float = 7.0,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Grouped decode-matmul over q4f16_1-layout experts: ``w_pre`` [E, N, K/8] words from
+    :func:`preprocess_weight_q4f16`, ``scales`` fp16 [E, N, K/g]."""
+    if out is None:
+        out = torch.empty(x.shape[0], w_pre.shape[1], dtype=torch.float16, device=x.device)
+    get_global_func("relax_b200.moe_gemm_q4f16")(x, w_pre, scales, zeros, indptr, int(group_size),
+                                                 float(zero_const), out)
+    return out
