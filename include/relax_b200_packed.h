@@ -99,6 +99,14 @@ RB200_API int RB200FuncListGlobalNames(int* out_size, const char*** out_array);
  *      the decode + matmul of test_gpu_gemv.py:193-206 with fp32 accumulation.
  *  "relax_b200.dequantize"(w_pre, scales, zeros|null, layout:int, weight_bits:int, group_size:int,
  *       zero_const:float, out fp16 [N, K])        verification aid.
+ *  "cutlass.group_gemm_fp16_sm90"(x f16 [M, K], weight f16 [E, N, K], indptr i64 [E] (device, end
+ *       rows), workspace u8 [..]|null, out f16 [M, N])
+ *      name and argument list of src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64.
+ *  "cutlass.moe_gemm"(x, w_pre i8 [E, K, N/2] | [E, K, N], scales f16 [E, K/g, N] | [E, N],
+ *       zeros|null, indptr i64 [E], workspace|null, out)
+ *      the same grouping over FT-layout quantised experts (no counterpart in the reference).
+ *  "relax_b200.moe_gemm_q4f16"(x, w_pre [E, N, K/8] words, scales f16 [E, N, K/g], zeros|null,
+ *       indptr i64 [E], group_size:int, zero_const:float, out)
  *  "runtime.get_cuda_stream"() -> handle          src/runtime/cuda/cuda_device_api.cc:318-320
  *  "runtime.set_cuda_stream"(handle)
  */
