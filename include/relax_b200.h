@@ -46,6 +46,8 @@ RB200_API int rb200_check_async_error(void* stream, int* status_out);
 /* Source layouts accepted by rb200_preprocess_weight. */
 #define RB200_LAYOUT_FT_KN 0 /* int8 container [K, N/2] (int4, low nibble = even column) or [K, N] (int8), signed codes */
 #define RB200_LAYOUT_Q4_NK 1 /* uint32 [N, K/8], nibble j of a word = element 8*word + j, unsigned codes */
+#define RB200_LAYOUT_AUTOGPTQ_KN 2 /* uint32 [K/8, N], nibble j of word (k/8, n) = element k = 8*(k/8) + j, unsigned
+                                      codes (tests/python/dlight/test_gpu_gemv.py:639-649) */
 
 /*
  * Repack a packed int4/int8 weight into the kernel-private fragment layout; the result has
@@ -60,6 +62,16 @@ RB200_API int rb200_check_async_error(void* stream, int* status_out);
  */
 RB200_API int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int64_t k,
                                       int64_t n, int is_int4, int src_layout, void* stream);
+
+/*
+ * AutoGPTQ zero points (tests/python/dlight/test_gpu_gemv.py:639-649): zq uint32
+ * [groups, n/8], nibble j of word (g, n/8) = column 8*(n/8) + j.  Writes fp16 [groups, n] holding
+ * f16(zq) + f16(1) - the value that decode subtracts - ready to be passed as the `zeros` tensor
+ * of rb200_gemm_fp16_intx with scale_stride_n = 1, scale_stride_g = n.  The matmul entries take
+ * groups in order along k (g_idx[k] = k / group_size); an arbitrary g_idx permutation is not
+ * supported.
+ */
+RB200_API int rb200_unpack_zeros_autogptq(const void* zq, void* zeros_out, int64_t groups, int64_t n, void* stream);
 
 /* ------------------------------------------------------------------ dequantize-matmul */
 

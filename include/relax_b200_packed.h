@@ -99,6 +99,10 @@ RB200_API int RB200FuncListGlobalNames(int* out_size, const char*** out_array);
  *      the decode + matmul of test_gpu_gemv.py:193-206 with fp32 accumulation.
  *  "relax_b200.dequantize"(w_pre, scales, zeros|null, layout:int, weight_bits:int, group_size:int,
  *       zero_const:float, out fp16 [N, K])        verification aid.
+ *  "relax_b200.preprocess_weight_autogptq"(qweight u32 [K/8, N], out)   AutoGPTQ source layout
+ *  "relax_b200.unpack_zeros_autogptq"(qzeros u32 [G, N/8], out f16 [G, N])   f16(zq) + 1
+ *  "relax_b200.gemm_fp16_autogptq"(x, w_pre, scales f16 [G, N], zeros f16 [G, N], bias|null, out)
+ *      the decode + matmul + add of tests/python/dlight/test_gpu_gemv.py:639-661, fp32 accumulation.
  *  "cutlass.group_gemm_fp16_sm90"(x f16 [M, K], weight f16 [E, N, K], indptr i64 [E] (device, end
  *       rows), workspace u8 [..]|null, out f16 [M, N])
  *      name and argument list of src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64.

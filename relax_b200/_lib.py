@@ -84,6 +84,7 @@ SIGNATURES = {
     "rb200_get_stream": (_V, []),
     "rb200_check_async_error": (_I, [_V, ctypes.POINTER(_I)]),
     "rb200_preprocess_weight": (_I, [_V, _V, _I64, _I64, _I64, _I, _I, _V]),
+    "rb200_unpack_zeros_autogptq": (_I, [_V, _V, _I64, _I64, _V]),
     "rb200_gemm_fp16_intx": (_I, [ctypes.POINTER(GemmDesc), _V]),
     "rb200_gemm_fp16_intx_noalloc": (_I, [ctypes.POINTER(GemmDesc), _V]),
     "rb200_gemm_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64, _I]),

@@ -239,11 +239,19 @@ int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int
   RB200_CHECK(n > 0 && k > 0 && n % 16 == 0 && k % frag == 0,
               "preprocess needs n %% 16 == 0 and k %% %d == 0 (n=%lld, k=%lld)", frag, (long long)n,
               (long long)k);
-  RB200_CHECK(src_layout == RB200_LAYOUT_FT_KN || (src_layout == RB200_LAYOUT_Q4_NK && is_int4),
+  RB200_CHECK(src_layout == RB200_LAYOUT_FT_KN ||
+                  ((src_layout == RB200_LAYOUT_Q4_NK || src_layout == RB200_LAYOUT_AUTOGPTQ_KN) && is_int4),
               "unsupported source layout %d for %d-bit weights", src_layout, bits);
   RB200_CHECK(aligned16(dst), "dst must be 16-byte aligned");
   return preprocess_launch(src, dst, num_experts, k, n, bits, src_layout,
                            static_cast<cudaStream_t>(stream));
+}
+
+int rb200_unpack_zeros_autogptq(const void* zq, void* zeros_out, int64_t groups, int64_t n, void* stream) {
+  RB200_CHECK(zq && zeros_out, "zq and zeros_out must be non-NULL");
+  RB200_CHECK(groups >= 1 && n >= 8 && n % 8 == 0, "need groups >= 1 and n %% 8 == 0 (groups=%lld, n=%lld)",
+              (long long)groups, (long long)n);
+  return unpack_zeros_autogptq_launch(zq, zeros_out, groups, n, static_cast<cudaStream_t>(stream));
 }
 
 size_t rb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int weight_bits) {

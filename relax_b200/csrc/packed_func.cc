@@ -143,6 +143,10 @@ int preprocess_common(const char* fn, const DLTensor* w, const DLTensor* out, bo
              "%s: FT weights must be int8", fn);
     k = rows;
     n = cols * (is_int4 ? 2 : 1);
+  } else if (layout == RB200_LAYOUT_AUTOGPTQ_KN) {
+    PF_CHECK(is_dtype(w, kDLUInt, 32) || is_dtype(w, kDLInt, 32), "%s: AutoGPTQ weights must be uint32 [K/8, N]", fn);
+    k = rows * 8;
+    n = cols;
   } else {
     PF_CHECK(is_dtype(w, kDLUInt, 32) || is_dtype(w, kDLInt, 32), "%s: q4f16 weights must be uint32", fn);
     n = rows;
@@ -198,6 +202,30 @@ int pf_preprocess_q4f16(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret
   if (a.tensor(0, &w) || a.tensor(1, &out)) return -1;
   if (ret_tc) *ret_tc = RB200_ARG_NULL;
   return preprocess_common(a.fname, w, out, true, RB200_LAYOUT_Q4_NK);
+}
+
+int pf_preprocess_autogptq(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "relax_b200.preprocess_weight_autogptq"};
+  const DLTensor *w, *out;
+  PF_CHECK(n == 2, "%s expects (qweight, out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &w) || a.tensor(1, &out)) return -1;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return preprocess_common(a.fname, w, out, true, RB200_LAYOUT_AUTOGPTQ_KN);
+}
+// (qzeros u32 [G, N/8], out f16 [G, N])
+int pf_unpack_zeros_autogptq(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "relax_b200.unpack_zeros_autogptq"};
+  const DLTensor *zq, *out;
+  PF_CHECK(n == 2, "%s expects (qzeros, out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &zq) || a.tensor(1, &out)) return -1;
+  PF_CHECK(zq->ndim == 2 && (is_dtype(zq, kDLUInt, 32) || is_dtype(zq, kDLInt, 32)) && compact(zq) &&
+               zq->device.device_type == kDLCUDA,
+           "%s: qzeros must be a compact uint32 [G, N/8] CUDA tensor", a.fname);
+  if (check_tensor(a.fname, "out", out, kDLFloat, 16)) return -1;
+  PF_CHECK(out->ndim == 2 && out->shape[0] == zq->shape[0] && out->shape[1] == zq->shape[1] * 8,
+           "%s: out must be fp16 [G, N]", a.fname);
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_unpack_zeros_autogptq(data_of(zq), data_of(out), zq->shape[0], out->shape[1], rb200_get_stream());
 }
 
 // ------------------------------------------------------------------ GEMM shims
@@ -357,6 +385,57 @@ int pf_gemm_q4f16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, 
 }
 
 // (w_pre, scales, zeros|null, layout, weight_bits, group_size, zero_const, out fp16 [N, K])
+// AutoGPTQ form (tests/python/dlight/test_gpu_gemv.py:639-661):
+// (x, w_pre u32 [K/8, N], scales f16 [G, N], zeros f16 [G, N] (from unpack_zeros_autogptq), bias|null, out)
+// out = bias + x @ ((q - zeros) * scales), groups in order along k (group size K / G).
+int pf_gemm_autogptq(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
+  const char* fname = "relax_b200.gemm_fp16_autogptq";
+  Args a{v, tc, n_args, fname};
+  PF_CHECK(n_args == 6, "%s expects 6 arguments, got %d", fname, n_args);
+  const DLTensor *x, *w, *s, *z, *bias, *out;
+  if (a.tensor(0, &x) || a.tensor(1, &w) || a.tensor(2, &s) || a.tensor(3, &z) || a.tensor(4, &bias, true) ||
+      a.tensor(5, &out))
+    return -1;
+  if (check_tensor(fname, "x", x, kDLFloat, 16) || check_tensor(fname, "scales", s, kDLFloat, 16) ||
+      check_tensor(fname, "zeros", z, kDLFloat, 16) || check_tensor(fname, "out", out, kDLFloat, 16))
+    return -1;
+  PF_CHECK(w->ndim == 2 && w->dtype.bits == 32 && compact(w) && w->device.device_type == kDLCUDA,
+           "%s: weight must be a compact uint32 [K/8, N] CUDA tensor", fname);
+  const int64_t k = w->shape[0] * 8, n = w->shape[1];
+  PF_CHECK(x->ndim >= 1 && x->shape[x->ndim - 1] == k, "%s: x inner extent != k=%lld", fname, (long long)k);
+  const int64_t m = lead_rows(x);
+  PF_CHECK(numel(out) == m * n, "%s: out has %lld elements, expected %lld", fname, (long long)numel(out),
+           (long long)(m * n));
+  PF_CHECK(s->ndim == 2 && s->shape[1] == n && s->shape[0] >= 1 && k % s->shape[0] == 0,
+           "%s: scales must be [G, N] with G dividing k", fname);
+  PF_CHECK(numel(z) == numel(s), "%s: zeros must have the shape of scales", fname);
+  rb200_gemm_desc d;
+  memset(&d, 0, sizeof(d));
+  d.struct_size = sizeof(d);
+  d.weight_bits = 4;
+  d.x = data_of(x);
+  d.w = data_of(w);
+  d.scales = data_of(s);
+  d.zeros = data_of(z);
+  if (bias) {
+    if (check_tensor(fname, "bias", bias, kDLFloat, 16)) return -1;
+    PF_CHECK(numel(bias) == n || numel(bias) == m * n, "%s: bias must be [n] or [m, n]", fname);
+    d.bias = data_of(bias);
+    d.bias_stride = (numel(bias) == n) ? 0 : n;
+  }
+  d.out = data_of(out);
+  d.m = m;
+  d.n = n;
+  d.k = k;
+  d.ldx = k;
+  d.ldo = n;
+  d.group_size = k / s->shape[0];
+  d.scale_stride_n = 1;
+  d.scale_stride_g = n;
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_gemm_fp16_intx(&d, rb200_get_stream());
+}
+
 // ------------------------------------------------------------------ grouped GEMM
 // cutlass.group_gemm_fp16_sm90(x [M,K] f16, weight [E,N,K] f16, indptr [E] i64, workspace [..] u8, out [M,N] f16):
 // the argument list of tvm_cutlass_group_gemm_sm90 (src/runtime/contrib/cutlass/fp16_group_gemm.cu:41-62).
@@ -541,6 +620,9 @@ void ensure_builtins() {
   done = true;
   register_builtin("cutlass.ft_preprocess_weight", pf_ft_preprocess_weight);
   register_builtin("relax_b200.preprocess_weight_q4f16", pf_preprocess_q4f16);
+  register_builtin("relax_b200.preprocess_weight_autogptq", pf_preprocess_autogptq);
+  register_builtin("relax_b200.unpack_zeros_autogptq", pf_unpack_zeros_autogptq);
+  register_builtin("relax_b200.gemm_fp16_autogptq", pf_gemm_autogptq);
   register_builtin("cutlass.ft_gemm_fp16_int4", pf_ft_gemm_int4);
   register_builtin("cutlass.ft_gemm_fp16_int8", pf_ft_gemm_int8);
   register_builtin("relax_b200.gemm_fp16_q4f16", pf_gemm_q4f16);

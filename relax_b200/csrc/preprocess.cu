@@ -19,9 +19,25 @@ __device__ __forceinline__ uint32_t load_code(const uint8_t* src, int64_t n, int
     }
     return (uint32_t)src[k * N + n] ^ 0x80u;  // signed byte + 128
   }
+  if (LAYOUT == 2) {  // AutoGPTQ: uint32 [K/8, N], nibble j of word (k/8, n) = element k = 8*(k/8) + j
+    const uint32_t w = reinterpret_cast<const uint32_t*>(src)[(k >> 3) * N + n];
+    return (w >> ((k & 7) * 4)) & 15u;
+  }
   // q4f16_1: uint32 [N, K/8], nibble j of a word = element 8*word + j, unsigned
   uint32_t b = src[n * (K / 2) + (k >> 1)];
   return (b >> ((k & 1) * 4)) & 15u;
+}
+
+// AutoGPTQ zero points: zq uint32 [G, N/8] (nibble j of word (g, n/8) = column 8*(n/8) + j) ->
+// fp16 [G, N] holding f16(zq) + f16(1), the value the decode subtracts
+// (tests/python/dlight/test_gpu_gemv.py:648).
+__global__ void unpack_zeros_autogptq_kernel(const uint32_t* __restrict__ zq, __half* __restrict__ out, int64_t total,
+                                             int64_t N) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t g = i / N, n = i % N;
+    const uint32_t q = (zq[g * (N / 8) + (n >> 3)] >> ((n & 7) * 4)) & 15u;
+    out[i] = __hadd(__int2half_rn((int)q), __float2half_rn(1.0f));
+  }
 }
 
 template <int BITS, int LAYOUT>
@@ -88,10 +104,23 @@ int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, in
     repack_kernel<4, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
   else if (bits == 4 && layout == 1)
     repack_kernel<4, 1><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+  else if (bits == 4 && layout == 2)
+    repack_kernel<4, 2><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
   else if (bits == 8 && layout == 0)
     repack_kernel<8, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
   else
     RB200_CHECK(false, "unsupported preprocess combination bits=%d layout=%d", bits, layout);
+  RB200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int unpack_zeros_autogptq_launch(const void* zq, void* out, int64_t groups, int64_t n, cudaStream_t stream) {
+  const int64_t total = groups * n;
+  if (total == 0) return 0;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  unpack_zeros_autogptq_kernel<<<(int)blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(zq),
+                                                               static_cast<__half*>(out), total, n);
   RB200_CUDA(cudaGetLastError());
   return 0;
 }

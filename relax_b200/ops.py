@@ -10,6 +10,7 @@ from .packed_func import get_global_func
 
 LAYOUT_FT_KN = 0
 LAYOUT_Q4_NK = 1
+LAYOUT_AUTOGPTQ_KN = 2
 
 
 def preprocess_weight_ft(packed_weight: torch.Tensor, is_int4: bool, sm: int = 100) -> torch.Tensor:
@@ -95,4 +96,35 @@ def moe_gemm_q4f16(x, w_pre, scales, indptr, zeros=None, group_size: int = 32, z
         out = torch.empty(x.shape[0], w_pre.shape[1], dtype=torch.float16, device=x.device)
     get_global_func("relax_b200.moe_gemm_q4f16")(x, w_pre, scales, zeros, indptr, int(group_size),
                                                  float(zero_const), out)
+    return out
+
+
+def preprocess_weight_autogptq(qweight: torch.Tensor) -> torch.Tensor:
+    """Repack an AutoGPTQ weight (uint32 [K/8, N], 8 k-consecutive nibbles per word:
+    tests/python/dlight/test_gpu_gemv.py:639-649)."""
+    return get_global_func("relax_b200.preprocess_weight_autogptq")(qweight)
+
+
+def unpack_zeros_autogptq(qzeros: torch.Tensor) -> torch.Tensor:
+    """AutoGPTQ zero points uint32 [G, N/8] -> fp16 [G, N] holding ``f16(zq) + 1``, the value the
+    reference's decode subtracts (tests/python/dlight/test_gpu_gemv.py:648)."""
+    out = torch.empty(qzeros.shape[0], qzeros.shape[1] * 8, dtype=torch.float16, device=qzeros.device)
+    get_global_func("relax_b200.unpack_zeros_autogptq")(qzeros, out)
+    return out
+
+
+def gemm_fp16_autogptq(x, w_pre, scales, zeros, bias=None, g_idx=None,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``bias + x @ ((q - zeros) * scales)`` for AutoGPTQ weights: ``w_pre`` from
+    :func:`preprocess_weight_autogptq`, ``scales`` fp16 [G, N], ``zeros`` fp16 [G, N] from
+    :func:`unpack_zeros_autogptq`.  Groups run in order along k; a ``g_idx`` that is not
+    ``k // group_size`` (activation reordering) is rejected."""
+    k, n = w_pre.shape[0] * 8, w_pre.shape[1]
+    if g_idx is not None:
+        expect = torch.arange(k, device=g_idx.device) // (k // scales.shape[0])
+        if not torch.equal(g_idx.to(torch.int64), expect):
+            raise ValueError("g_idx must be k // group_size: reordered groups are not supported")
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n, dtype=torch.float16, device=x.device)
+    get_global_func("relax_b200.gemm_fp16_autogptq")(x, w_pre, scales, zeros, bias, out)
     return out

@@ -124,7 +124,8 @@ def _wrap_preprocess(pf: PackedFunc) -> Callable:
     return call
 
 
-_ALLOCATING = {"cutlass.ft_preprocess_weight", "relax_b200.preprocess_weight_q4f16"}
+_ALLOCATING = {"cutlass.ft_preprocess_weight", "relax_b200.preprocess_weight_q4f16",
+               "relax_b200.preprocess_weight_autogptq"}
 _CACHE = {}
 
 
