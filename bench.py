@@ -201,6 +201,10 @@ def run_gpu(args):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
+    # serving-loop setting: weights are resident and never rewritten, so consecutive decode kernels
+    # may overlap their launch and weight streaming with the previous kernel's tail
+    relax_b200.set_launch_overlap(os.environ.get("RB200_BENCH_NO_OVERLAP", "0") != "1")
+
     gen = torch.Generator(device=dev)
     gen.manual_seed(1000 + rank)
     lin = linears()
@@ -436,7 +440,8 @@ def run_gpu(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": dict(workload_config(world), timed_with="cuda graph replay" if graphs else "eager launches"),
+            "config": dict(workload_config(world), timed_with="cuda graph replay" if graphs else "eager launches",
+                           launch_overlap=relax_b200.get_launch_overlap()),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,

@@ -41,6 +41,20 @@ RB200_API void* rb200_get_stream(void);
  */
 RB200_API int rb200_check_async_error(void* stream, int* status_out);
 
+/*
+ * Launch overlap for serving loops (process-wide switch, default off; no counterpart in the
+ * reference, whose generated host code launches every kernel fully stream-ordered).  When on,
+ * the decode-path matmul kernels (m <= 32) are launched as programmatic dependents: a kernel may
+ * become resident and start streaming its WEIGHT, SCALE and ZERO-POINT tensors while the previous
+ * kernel on the stream is still finishing; it reads x / bias / residual and writes out / scratch
+ * only after that kernel has completed, so activations stay ordered as before.
+ * Contract when on: the weight, scale and zero-point tensors passed to a matmul call were not
+ * written by the kernel immediately before it on the same stream (repack weights ahead of time,
+ * or synchronise once after preprocessing).  Works inside CUDA-graph capture.
+ */
+RB200_API int rb200_set_launch_overlap(int enabled);
+RB200_API int rb200_get_launch_overlap(void);
+
 /* ------------------------------------------------------------------ weight preprocess */
 
 /* Source layouts accepted by rb200_preprocess_weight. */

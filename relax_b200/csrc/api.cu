@@ -2,6 +2,7 @@
 // No entry point here allocates after its first call on a device, synchronises, or falls back
 // to a host computation.
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/relax_b200.h"
@@ -197,7 +198,18 @@ int validate_common(const rb200_gemm_desc* d) {
 
 using namespace rb200;
 
+namespace rb200 {
+static std::atomic<int> g_launch_overlap{0};
+bool launch_overlap_enabled() { return g_launch_overlap.load(std::memory_order_relaxed) != 0; }
+}  // namespace rb200
+
 extern "C" {
+
+int rb200_set_launch_overlap(int enabled) {
+  g_launch_overlap.store(enabled ? 1 : 0, std::memory_order_relaxed);
+  return 0;
+}
+int rb200_get_launch_overlap(void) { return launch_overlap_enabled() ? 1 : 0; }
 
 const char* rb200_last_error(void) { return g_last_error.c_str(); }
 

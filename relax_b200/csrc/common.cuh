@@ -49,6 +49,11 @@ struct DeviceScratch {
 // call once during warm-up).  nullptr + last error set on failure.
 DeviceScratch* device_scratch(size_t min_partial_bytes, size_t min_counter_ints);
 
+// Launch overlap (programmatic dependent launch): when the host enabled it, matmul kernels are
+// launched so that they may start - and stream their weights - while the previous kernel on the
+// stream is still finishing.  See rb200_set_launch_overlap in the public header.
+bool launch_overlap_enabled();
+
 // Status codes written to the device status word.
 enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadConfig = 2 };
 
@@ -164,6 +169,16 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+
+// Programmatic dependent launch.  launch_dependents: the next kernel on the stream may begin
+// once every CTA of this grid has executed it (or exited).  wait: blocks until the kernels this
+// grid depends on have completed and their memory is visible; returns at once for an ordinary
+// launch.  Everything the previous kernel may have produced (activations) is read after wait,
+// and every global write of this grid (outputs, scratch) comes after it too.
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t ld_nc_u16(const __half* p) {
   unsigned short v;

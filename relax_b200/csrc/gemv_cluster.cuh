@@ -178,6 +178,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   fence_proxy_async();
   __syncthreads();
   if (S > 1) cluster_sync_all();  // peers' mbarriers exist before anyone arrives on them
+  griddep_launch_dependents();
 
   const int cpt = p.chunks_per_tile;
   const int c0 = (int)((long long)rank * cpt / S);
@@ -191,6 +192,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    bool dep_waited = false;
     for (int tile = cluster_id; tile < n_tiles && ok; tile += n_clusters) {
       const int blk0 = tile * kConsumerWarps;
       const int nblk = min(kConsumerWarps, n_blocks - blk0);
@@ -224,6 +226,11 @@ __global__ void __launch_bounds__(kThreads, 2)
             if (SRC == kSrcSmemNK) tma_load_2d(sbase + L::kZOff, &tmap_z, gc0, blk0 * 16, &full_bar[stage]);
             else tma_load_2d(sbase + L::kZOff, &tmap_z, blk0 * 16, gc0, &full_bar[stage]);
           }
+        }
+        // activations may come from the previous kernel on the stream: read them after it ended
+        if (!dep_waited) {
+          griddep_wait();
+          dep_waited = true;
         }
         for (int r = lane; r < p.m; r += 32) {
           const __half* src = p.x + (size_t)r * p.ldx + (size_t)kb0 * G::kFrag;
@@ -447,6 +454,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
     }
     if (store && active) {
+      griddep_wait();  // the previous kernel may still read what this store overwrites
       const int64_t n0 = (int64_t)blk * 16 + g;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {

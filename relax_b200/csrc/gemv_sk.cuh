@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   }
   fence_proxy_async();
   __syncthreads();
+  griddep_launch_dependents();
 
 #ifdef RB200_ABLATE
   const int ablate = p.ablate;
@@ -226,6 +227,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
     bool ok = true;
     const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
     constexpr int kXChunks = G::kChunk * 2 / 16;  // 16-byte pieces per x row per stage (32 / 16)
+    bool dep_waited = false;
     for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, pc); ++idx) {
       const int64_t n0 = (int64_t)pc.tile * kTileRows;
       for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
@@ -234,13 +236,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
           break;
         }
         uint8_t* sbase = smem + (size_t)stage * kStage;
-        // x[r, chunk*kChunk + c*8 .. +8) -> row r of the stage's x tile
-        for (int i = lane; i < p.m * kXChunks; i += 32) {
-          const int r = i / kXChunks, c = i % kXChunks;
-          const int64_t kcol = (int64_t)chunk * G::kChunk + c * 8;
-          const uint32_t v = kcol < p.k ? 16u : 0u;
-          cp_async16(sbase + G::kWBytes + r * G::kXPitch + c * 16, p.x + (int64_t)r * p.ldx + (v ? kcol : 0), v);
-        }
         if (SRC == kSrcSmemNK) {
           // [128 rows][8 groups]: 16 bytes per row
           const int64_t g0 = (int64_t)chunk * 8;
@@ -265,6 +260,18 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
             cp_async16(sbase + L::kSOff + gl * 256 + cc * 16, p.s + o, in ? 16u : 0u);
             if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + L::kZOff + gl * 256 + cc * 16, p.z + o, in ? 16u : 0u);
           }
+        }
+        // activations may come from the previous kernel on the stream: read them after it ended
+        if (!dep_waited) {
+          griddep_wait();
+          dep_waited = true;
+        }
+        // x[r, chunk*kChunk + c*8 .. +8) -> row r of the stage's x tile
+        for (int i = lane; i < p.m * kXChunks; i += 32) {
+          const int r = i / kXChunks, c = i % kXChunks;
+          const int64_t kcol = (int64_t)chunk * G::kChunk + c * 8;
+          const uint32_t v = kcol < p.k ? 16u : 0u;
+          cp_async16(sbase + G::kWBytes + r * G::kXPitch + c * 16, p.x + (int64_t)r * p.ldx + (v ? kcol : 0), v);
         }
         cp_async_arrive(&full_bar[stage]);
         if (++stage == stages) {
@@ -478,6 +485,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) fin[mt][c] = acc[mt][0][c];
 
+    // outputs and scratch may still be in use by the previous kernel until it has ended
+    griddep_wait();
     if (pc.kind == kWhole) {
       store_tile(fin, pc.tile);
     } else if (pc.kind == kHead) {
