@@ -319,6 +319,7 @@ def run_gpu(args):
         copies = max(2, int(320e6 // wbytes) + 1)
         pres = [pre0.clone() for _ in range(copies)]
         scs = [sc0.clone() for _ in range(copies)]
+        torch.cuda.synchronize()  # weights are complete before any overlapped launch reads them
         for m in MS:
             def run_all():
                 for c_ in range(copies):
