@@ -205,6 +205,16 @@ def run_gpu(args):
     # may overlap their launch and weight streaming with the previous kernel's tail
     relax_b200.set_launch_overlap(os.environ.get("RB200_BENCH_NO_OVERLAP", "0") != "1")
 
+    # row-parallel outputs ([M, 4096] fp16, at most 256 KiB): the library's one-shot all-reduce over
+    # CUDA IPC workspaces; RB200_BENCH_NCCL_ALLREDUCE=1 times NCCL's instead
+    allreduce = None
+    if world > 1:
+        if os.environ.get("RB200_BENCH_NCCL_ALLREDUCE", "0") == "1":
+            allreduce = lambda t: dist.all_reduce(t)
+        else:
+            from relax_b200.sharding import OneShotAllReduce
+            allreduce = OneShotAllReduce(max(MS) * 4096)
+
     gen = torch.Generator(device=dev)
     gen.manual_seed(1000 + rank)
     lin = linears()
@@ -258,7 +268,7 @@ def run_gpu(args):
                     e1.record()
                     events.append((e0, e1, synth.algorithmic_bytes(m, n, k, 4, GROUP)))
                 if world > 1 and name in row_parallel:
-                    dist.all_reduce(outs[(name, m)])
+                    allreduce(outs[(name, m)])
 
     def barrier():
         if world > 1:
@@ -398,7 +408,7 @@ def run_gpu(args):
                 xs[(name, m)].copy_(hx[(name, m)], non_blocking=True)
                 ops.gemm_fp16_q4f16(xs[(name, m)], pre, sc, out=outs[(name, m)])
                 if world > 1 and name in row_parallel:
-                    dist.all_reduce(outs[(name, m)])
+                    allreduce(outs[(name, m)])
                 hout[(name, m)].copy_(outs[(name, m)], non_blocking=True)
         torch.cuda.synchronize()  # the step's results are on the host
 

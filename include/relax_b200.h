@@ -211,6 +211,43 @@ typedef struct rb200_group_gemm_desc {
 } rb200_group_gemm_desc;
 RB200_API int rb200_group_gemm(const rb200_group_gemm_desc* desc, void* stream);
 
+/* ------------------------------------------------------------------ low-latency all-reduce */
+
+/*
+ * Sum all-reduce of small fp16 tensors across the GPUs of one node (the partial outputs of a
+ * row-parallel matmul at decode batch sizes), one kernel per rank, peers' partial sums pulled
+ * over NVLink.  Replaces the one-shot strategy of runtime.disco.cuda_ipc.custom_allreduce
+ * (src/runtime/disco/cuda_ipc/custom_allreduce.cc:65-105; kernels in
+ * 3rdparty/tensorrt_llm/custom_allreduce_kernels.cu:120-264).  Messages above the workspace's
+ * max_count belong on NCCL, as in the reference (custom_allreduce.cc:69-76).
+ *
+ * Set-up (once per process group, mirrors src/runtime/disco/cuda_ipc/cuda_ipc_memory.cc):
+ *   every rank:  rb200_peer_alloc(rb200_allreduce_workspace_bytes(max_count), &ws)   zero-filled
+ *                rb200_peer_export(ws, handle)  -> exchange the 64-byte handles by any host channel
+ *                rb200_peer_import(handle_of_rank_p, &ws_p) for every p != rank
+ *   then a host barrier, so that no rank starts before all workspaces exist.
+ * Call: workspaces[p] = this process's address of rank p's workspace (own pointer at [rank]).
+ * All ranks must issue the same sequence of calls (same count each time).  in / out are ordinary
+ * device tensors of `count` fp16 elements, 16-byte aligned; in == out is allowed.  The result is
+ * bit-identical on every rank (fixed summation order, fp32 accumulation, one rounding).
+ * A peer that never arrives makes the bounded wait give up after about two seconds: the status
+ * word read by rb200_check_async_error becomes non-zero and `out` is left unwritten.
+ * Works under CUDA-graph capture (the call number is kept on the device).
+ */
+#define RB200_PEER_HANDLE_BYTES 64
+RB200_API size_t rb200_allreduce_workspace_bytes(int64_t max_count);
+RB200_API int rb200_allreduce_oneshot(void* const* workspaces, int rank, int world, const void* in, void* out,
+                                      int64_t count, int64_t max_count, void* stream);
+/* Single-GPU self-test of the same kernel: all `world` ranks run inside one cooperative launch on
+ * the current device (workspaces, ins and outs are `world` local buffers). */
+RB200_API int rb200_allreduce_oneshot_selftest(void* const* workspaces, const void* const* ins, void* const* outs,
+                                               int world, int64_t count, int64_t max_count, void* stream);
+RB200_API int rb200_peer_alloc(size_t bytes, void** ptr);
+RB200_API int rb200_peer_free(void* ptr);
+RB200_API int rb200_peer_export(void* ptr, void* handle_out /* RB200_PEER_HANDLE_BYTES */);
+RB200_API int rb200_peer_import(const void* handle, void** ptr);
+RB200_API int rb200_peer_close(void* ptr);
+
 /*
  * Debug/verification entry: writes the dequantised weight wq fp16 [n, k] (row-major) that the
  * matmul kernels feed to the tensor cores, produced by the same device decode routine.  Uses

@@ -96,6 +96,15 @@ SIGNATURES = {
                                                    _I, _I, _V, ctypes.c_size_t, _V]),
     "rb200_dequantize": (_I, [ctypes.POINTER(GemmDesc), _V, _V]),
     "rb200_group_gemm": (_I, [ctypes.POINTER(GroupGemmDesc), _V]),
+    "rb200_allreduce_workspace_bytes": (ctypes.c_size_t, [_I64]),
+    "rb200_allreduce_oneshot": (_I, [ctypes.POINTER(_V), _I, _I, _V, _V, _I64, _I64, _V]),
+    "rb200_allreduce_oneshot_selftest": (_I, [ctypes.POINTER(_V), ctypes.POINTER(_V), ctypes.POINTER(_V), _I,
+                                              _I64, _I64, _V]),
+    "rb200_peer_alloc": (_I, [ctypes.c_size_t, ctypes.POINTER(_V)]),
+    "rb200_peer_free": (_I, [_V]),
+    "rb200_peer_export": (_I, [_V, _V]),
+    "rb200_peer_import": (_I, [_V, ctypes.POINTER(_V)]),
+    "rb200_peer_close": (_I, [_V]),
     "RB200FuncGetGlobal": (_I, [_S, ctypes.POINTER(_V)]),
     "RB200FuncCall": (_I, [_V, ctypes.POINTER(Value), ctypes.POINTER(_I), _I,
                            ctypes.POINTER(Value), ctypes.POINTER(_I)]),

@@ -91,3 +91,76 @@ def allreduce_sum_(t, group=None):
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     return t
+
+
+class OneShotAllReduce:
+    """Low-latency sum all-reduce of small fp16 tensors between the GPUs of one node
+    (``rb200_allreduce_oneshot``): the counterpart of ``runtime.disco.cuda_ipc.custom_allreduce``
+    with its one-shot strategy (src/runtime/disco/cuda_ipc/custom_allreduce.cc:65-105).  Each rank
+    allocates a peer-visible workspace, the ranks exchange its CUDA IPC handle over
+    ``torch.distributed`` (any backend - only host bytes travel) and map one another's
+    (src/runtime/disco/cuda_ipc/cuda_ipc_memory.cc does the same with Disco's channel).
+
+    ``max_count`` bounds the tensor size in elements; larger tensors go through
+    :func:`allreduce_sum_` (NCCL), as the reference falls back to ``ncclAllReduce``.
+    All ranks must call with the same sequence of tensor sizes."""
+
+    def __init__(self, max_count: int, group=None):
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        from . import _lib
+        self._lib = _lib
+        lib = _lib.load()
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one node)")
+        self.max_count = int(max_count)
+        nbytes = lib.rb200_allreduce_workspace_bytes(self.max_count)
+        own = ctypes.c_void_p()
+        _lib.check(lib.rb200_peer_alloc(nbytes, ctypes.byref(own)))
+        self._own = own
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.rb200_peer_export(own, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._imported = []
+        ptrs = (ctypes.c_void_p * self.world)()
+        for p in range(self.world):
+            if p == self.rank:
+                ptrs[p] = own.value
+            else:
+                q = ctypes.c_void_p()
+                _lib.check(lib.rb200_peer_import(ctypes.create_string_buffer(handles[p], 64), ctypes.byref(q)))
+                self._imported.append(q)
+                ptrs[p] = q.value
+        self._ptrs = ptrs
+        dist.barrier(group=group)  # every workspace exists and is zero before the first call
+        self._torch = torch
+
+    def fits(self, t) -> bool:
+        return t.dtype == self._torch.float16 and t.is_contiguous() and t.numel() <= self.max_count
+
+    def __call__(self, t, out=None):
+        """In place by default.  ``t``: contiguous fp16 CUDA tensor of at most ``max_count`` elements."""
+        import ctypes
+        if not self.fits(t):
+            raise ValueError("tensor does not fit the one-shot all-reduce (fp16, contiguous, <= %d elements)"
+                             % self.max_count)
+        out = t if out is None else out
+        stream = self._torch.cuda.current_stream().cuda_stream
+        self._lib.check(self._lib.load().rb200_allreduce_oneshot(
+            self._ptrs, self.rank, self.world, ctypes.c_void_p(t.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+            t.numel(), self.max_count, ctypes.c_void_p(stream)))
+        return out
+
+    def close(self):
+        lib = self._lib.load()
+        for q in self._imported:
+            lib.rb200_peer_close(q)
+        self._imported = []
+        if self._own is not None:
+            lib.rb200_peer_free(self._own)
+            self._own = None
