@@ -205,15 +205,17 @@ def run_gpu(args):
     # may overlap their launch and weight streaming with the previous kernel's tail
     relax_b200.set_launch_overlap(os.environ.get("RB200_BENCH_NO_OVERLAP", "0") != "1")
 
-    # row-parallel outputs ([M, 4096] fp16, at most 256 KiB): the library's one-shot all-reduce over
-    # CUDA IPC workspaces; RB200_BENCH_NCCL_ALLREDUCE=1 times NCCL's instead
+    # row-parallel outputs ([M, 4096] fp16, at most 256 KiB): NCCL by default; RB200_BENCH_ONESHOT_ALLREDUCE=1
+    # uses the library's one-shot all-reduce over CUDA IPC workspaces instead
     allreduce = None
+    allreduce_kind = "none"
     if world > 1:
-        if os.environ.get("RB200_BENCH_NCCL_ALLREDUCE", "0") == "1":
-            allreduce = lambda t: dist.all_reduce(t)
-        else:
+        allreduce_kind = "nccl"
+        allreduce = lambda t: dist.all_reduce(t)
+        if os.environ.get("RB200_BENCH_ONESHOT_ALLREDUCE", "0") == "1":
             from relax_b200.sharding import OneShotAllReduce
             allreduce = OneShotAllReduce(max(MS) * 4096)
+            allreduce_kind = "one-shot (rb200_allreduce_oneshot)"
 
     gen = torch.Generator(device=dev)
     gen.manual_seed(1000 + rank)
@@ -452,7 +454,7 @@ def run_gpu(args):
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": dict(workload_config(world), timed_with="cuda graph replay" if graphs else "eager launches",
-                           launch_overlap=relax_b200.get_launch_overlap()),
+                           launch_overlap=relax_b200.get_launch_overlap(), allreduce=allreduce_kind),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,
