@@ -145,7 +145,10 @@ struct ScalePlan {
 };
 
 template <int BITS, int MT, int ZMODE, int GROUP, int SRC>
-__global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
+#ifndef RB200_SK_CTAS_MT1
+#define RB200_SK_CTAS_MT1 2
+#endif
+__global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gemv_sk_kernel(const Params pp) {
   using G = Geo<BITS>;
   using L = StageLayout<BITS, MT, ZMODE, SRC>;
   using SP = ScalePlan<BITS, GROUP>;
@@ -168,7 +171,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   }
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
+#ifdef RB200_SK_LAG
+      mbar_init(&full_bar[s], 2);
+#else
       mbar_init(&full_bar[s], 1 + 32);  // producer's expect_tx arrival + 32 loader lanes
+#endif
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
     mbar_fence_init();
@@ -228,6 +235,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
     const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
     constexpr int kXChunks = G::kChunk * 2 / 16;  // 16-byte pieces per x row per stage (32 / 16)
     bool dep_waited = false;
+#ifdef RB200_SK_LAG
+    int lag_issued = 0, lag_stage = 0;
+#endif
     for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, pc); ++idx) {
       const int64_t n0 = (int64_t)pc.tile * kTileRows;
       for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
@@ -273,7 +283,17 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
           const uint32_t v = kcol < p.k ? 16u : 0u;
           cp_async16(sbase + G::kWBytes + r * G::kXPitch + c * 16, p.x + (int64_t)r * p.ldx + (v ? kcol : 0), v);
         }
+#ifdef RB200_SK_LAG
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (++lag_issued > 2) {
+          asm volatile("cp.async.wait_group 2;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[lag_stage]);
+          if (++lag_stage == stages) lag_stage = 0;
+        }
+#else
         cp_async_arrive(&full_bar[stage]);
+#endif
         if (++stage == stages) {
           stage = 0;
           phase ^= 1u;
@@ -281,6 +301,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
+#ifdef RB200_SK_LAG
+    __syncwarp();
+    for (int i = lag_issued < 2 ? lag_issued : 2; i > 0; --i) {
+      if (lane == 0) mbar_arrive(&full_bar[lag_stage]);
+      if (++lag_stage == stages) lag_stage = 0;
+    }
+#endif
     return;
   }
 
