@@ -66,6 +66,12 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
   __shared__ uint32_t s_call;
   __shared__ int s_fail;
 
+  // Launch overlap: the next kernel on the stream (usually the next layer's matmul) may become
+  // resident next to these 32 small CTAs and stream its weights while the exchange runs; this
+  // kernel itself touches nothing - not even its call counters, which the previous all-reduce
+  // may still be updating - before everything ahead of it on the stream has completed.
+  griddep_launch_dependents();
+  griddep_wait();
   uint32_t* counters = reinterpret_cast<uint32_t*>(p.ws[r]);
   uint32_t* my_flags = counters + kMaxCtas;
   if (tid == 0) {
@@ -98,10 +104,12 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
       dst[u] = v;
     }
   }
-  __threadfence_system();
   __syncthreads();
-  // 2. tell every rank (this one included) that slice c of rank r is there; wait for the peers
+  // 2. tell every rank (this one included) that slice c of rank r is there; wait for the peers.
+  // One system-scope fence per signalling thread: the block barrier orders the other threads'
+  // stores before it (a fence in every thread costs several microseconds per call).
   if (tid < p.world) {
+    __threadfence_system();
     uint32_t* peer_flags = reinterpret_cast<uint32_t*>(p.ws[tid]) + kMaxCtas;
     st_release_sys(peer_flags + r * kMaxCtas + c, call);
   }
@@ -201,8 +209,17 @@ int rb200_allreduce_oneshot(void* const* workspaces, int rank, int world, const 
   p.count = count;
   p.region_bytes = region_bytes_for(max_count);
   p.status = sc->status;
-  allreduce_oneshot_kernel<<<dim3(grid_for(count), 1, 1), kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  RB200_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid_for(count), 1, 1);
+  cfg.blockDim = dim3(kArThreads, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = launch_overlap_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  RB200_CUDA(cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel, p));
   return 0;
 }
 
