@@ -99,7 +99,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    run_once, nbytes, threads, sample = cpu_sample(1.5)
+    # every step is a bounded sample; the whole run (warm-up + steps) is sized to about two minutes
+    run_once, nbytes, threads, sample = cpu_sample(max(0.02, min(1.5, 120.0 / max(1, args.steps + args.warmup))))
     for _ in range(args.warmup):
         run_once()
     t = 0.0

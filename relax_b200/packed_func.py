@@ -46,6 +46,27 @@ def as_dltensor(t: torch.Tensor, keep: list) -> DLTensor:
     return dl
 
 
+# DLTensor structs of recently seen tensors: a serving loop passes the same buffers on every step,
+# and building the ctypes structs costs more host time than a decode kernel runs.  Keyed by
+# everything the struct encodes; bounded.
+_DL_CACHE: dict = {}
+_DL_CACHE_MAX = 8192
+
+
+def _cached_dltensor(t: torch.Tensor):
+    key = (t.data_ptr(), tuple(t.shape), t.dtype, t.device.type, t.device.index,
+           None if t.is_contiguous() else tuple(t.stride()))
+    hit = _DL_CACHE.get(key)
+    if hit is not None:
+        return hit[0]
+    if len(_DL_CACHE) >= _DL_CACHE_MAX:
+        _DL_CACHE.clear()
+    keep: List[Any] = []
+    dl = as_dltensor(t, keep)
+    _DL_CACHE[key] = (dl, keep)
+    return dl
+
+
 class PackedFunc:
     """One global function of the registry (what ``TVMFuncGetGlobal`` hands back)."""
 
@@ -65,7 +86,7 @@ class PackedFunc:
                 values[i].v_handle = None
                 codes[i] = ARG_NULL
             elif isinstance(a, torch.Tensor):
-                dl = as_dltensor(a, keep)
+                dl = _cached_dltensor(a)
                 values[i].v_handle = ctypes.addressof(dl)
                 codes[i] = ARG_DLTENSOR
                 if a.is_cuda and cuda_dev is None:
@@ -86,11 +107,17 @@ class PackedFunc:
         ret = Value()
         ret_code = ctypes.c_int(ARG_NULL)
         if cuda_dev is not None or torch.cuda.is_available():
-            dev = cuda_dev if cuda_dev is not None else torch.device("cuda", torch.cuda.current_device())
-            with torch.cuda.device(dev):
-                lib.rb200_set_stream(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+            cur = torch.cuda.current_device()
+            dev_index = cur if cuda_dev is None or cuda_dev.index is None else cuda_dev.index
+            if dev_index == cur:
+                lib.rb200_set_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
                 rc = lib.RB200FuncCall(self.handle, values, codes, n, ctypes.byref(ret),
                                        ctypes.byref(ret_code))
+            else:
+                with torch.cuda.device(dev_index):
+                    lib.rb200_set_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                    rc = lib.RB200FuncCall(self.handle, values, codes, n, ctypes.byref(ret),
+                                           ctypes.byref(ret_code))
         else:
             rc = lib.RB200FuncCall(self.handle, values, codes, n, ctypes.byref(ret),
                                    ctypes.byref(ret_code))
