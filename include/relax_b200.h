@@ -211,6 +211,19 @@ typedef struct rb200_group_gemm_desc {
 } rb200_group_gemm_desc;
 RB200_API int rb200_group_gemm(const rb200_group_gemm_desc* desc, void* stream);
 
+/* ------------------------------------------------------------------ quantiser */
+
+/*
+ * The reference tests' encode step on the GPU (tests/python/relax/test_codegen_cutlass.py:1391-1457
+ * int4, :1630-1676 int8, :2043-2109 int8 in groups of 64), which the reference runs as a CPU
+ * transform_params stage: a fp16 [n, k] -> packed int8 [k, n/2] (int4, low nibble = even n) or
+ * [k, n] (int8) and scales fp16 [n] (group_size <= 0 or >= k) or [k/group_size, n];
+ * scale = max(absmax, 1e-4) / 8 (int4) or / 128 (int8) in fp32, codes rounded half away from zero
+ * and clipped.  The result feeds rb200_preprocess_weight (layout RB200_LAYOUT_FT_KN).
+ */
+RB200_API int rb200_encode_ft(const void* a, void* packed, void* scales, int64_t n, int64_t k, int weight_bits,
+                              int64_t group_size, void* stream);
+
 /* ------------------------------------------------------------------ low-latency all-reduce */
 
 /*

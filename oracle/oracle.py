@@ -241,7 +241,9 @@ def np_matmul_f32(x, w_nk):
 
 def _round_half_away(v):
     """T.round lowers to round-half-away-from-zero (llvm.round), unlike numpy's half-to-even."""
-    return np.sign(v) * np.floor(np.abs(v) + np.float32(0.5))
+    # in float64 so that |v| + 0.5 is exact for float32 inputs (0.49999997 must round to 0)
+    v64 = np.asarray(v, dtype=np.float64)
+    return (np.sign(v64) * np.floor(np.abs(v64) + 0.5)).astype(np.float32)
 
 
 def np_encode_ft(y, bits, group=-1):

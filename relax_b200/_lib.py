@@ -86,6 +86,7 @@ SIGNATURES = {
     "rb200_set_launch_overlap": (_I, [_I]),
     "rb200_get_launch_overlap": (_I, []),
     "rb200_preprocess_weight": (_I, [_V, _V, _I64, _I64, _I64, _I, _I, _V]),
+    "rb200_encode_ft": (_I, [_V, _V, _V, _I64, _I64, _I, _I64, _V]),
     "rb200_unpack_zeros_autogptq": (_I, [_V, _V, _I64, _I64, _V]),
     "rb200_gemm_fp16_intx": (_I, [ctypes.POINTER(GemmDesc), _V]),
     "rb200_gemm_fp16_intx_noalloc": (_I, [ctypes.POINTER(GemmDesc), _V]),

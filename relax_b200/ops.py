@@ -128,3 +128,20 @@ def gemm_fp16_autogptq(x, w_pre, scales, zeros, bias=None, g_idx=None,
         out = torch.empty(*x.shape[:-1], n, dtype=torch.float16, device=x.device)
     get_global_func("relax_b200.gemm_fp16_autogptq")(x, w_pre, scales, zeros, bias, out)
     return out
+
+
+def encode_ft(y: torch.Tensor, weight_bits: int, group_size: int = -1):
+    """The reference tests' quantiser on the GPU (tests/python/relax/test_codegen_cutlass.py:1391-1457,
+    :1630-1676, :2043-2109): ``y`` fp16 [N, K] -> ``(packed int8 [K, N/2] | [K, N], scales fp16 [N] |
+    [K/group, N])``, ready for :func:`preprocess_weight_ft`."""
+    import ctypes
+    from . import _lib
+    n, k = y.shape
+    per_row = group_size <= 0 or group_size >= k
+    packed = torch.empty(k, n // 2 if weight_bits == 4 else n, dtype=torch.int8, device=y.device)
+    scales = torch.empty((n,) if per_row else (k // group_size, n), dtype=torch.float16, device=y.device)
+    y = y.contiguous()
+    _lib.check(_lib.load().rb200_encode_ft(ctypes.c_void_p(y.data_ptr()), ctypes.c_void_p(packed.data_ptr()),
+                                           ctypes.c_void_p(scales.data_ptr()), n, k, int(weight_bits),
+                                           int(group_size), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return packed, scales
