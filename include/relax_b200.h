@@ -211,6 +211,36 @@ typedef struct rb200_group_gemm_desc {
 } rb200_group_gemm_desc;
 RB200_API int rb200_group_gemm(const rb200_group_gemm_desc* desc, void* stream);
 
+/* ------------------------------------------------------------------ mixture-of-experts routing */
+
+/*
+ * The steps on either side of the grouped matmul.  The reference has no operator for them, only
+ * the primitives its models compose (stable sort by key, scan: src/runtime/contrib/thrust/thrust.cu:215,325);
+ * the row order and indptr convention are what cutlass.group_gemm_fp16_sm90 consumes
+ * (src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64).
+ *
+ * rb200_moe_route: logits fp32 [tokens, num_experts] (device) -> softmax, top_k experts per token
+ *   (equal probabilities: lower expert index first).  Assignments are numbered token-major,
+ *   flat = token * top_k + j; rows are the assignments stably sorted by expert.  Writes (device):
+ *     indptr       int64 [num_experts]      end row of every expert
+ *     token_of_row int32 [tokens * top_k]
+ *     gate_of_row  fp32  [tokens * top_k]   softmax probability of the assignment
+ *     row_of_flat  int32 [tokens * top_k]   where assignment `flat` went
+ *   workspace: rb200_moe_route_workspace_bytes(tokens, top_k) bytes of device memory.
+ *   num_experts <= 64, top_k <= 8.
+ * rb200_moe_gather:  out fp16 [rows, k] = x[token_of_row[row]].
+ * rb200_moe_combine: out fp16 [tokens, n] = f16( sum_j gate_of_row[r_j] * y[r_j] ), r_j =
+ *   row_of_flat[token * top_k + j], fp32 sum in j order (deterministic).
+ */
+RB200_API size_t rb200_moe_route_workspace_bytes(int64_t tokens, int64_t top_k);
+RB200_API int rb200_moe_route(const void* logits, int64_t tokens, int64_t num_experts, int64_t top_k, int64_t* indptr,
+                              int32_t* token_of_row, float* gate_of_row, int32_t* row_of_flat, void* workspace,
+                              size_t workspace_bytes, void* stream);
+RB200_API int rb200_moe_gather(const void* x, const int32_t* token_of_row, void* out, int64_t rows, int64_t k,
+                               void* stream);
+RB200_API int rb200_moe_combine(const void* y, const int32_t* row_of_flat, const float* gate_of_row, void* out,
+                                int64_t tokens, int64_t top_k, int64_t n, void* stream);
+
 /* ------------------------------------------------------------------ quantiser */
 
 /*

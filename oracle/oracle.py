@@ -270,3 +270,22 @@ def np_encode_ft(y, bits, group=-1):
         return qt, scales16
     packed = ((qt[:, 0::2].astype(np.int32) & 15) | ((qt[:, 1::2].astype(np.int32) & 15) << 4))
     return packed.astype(np.uint8).view(np.int8), scales16
+
+
+def np_moe_route(logits, top_k):
+    """Routing restatement: softmax, top-k (ties to the lower expert index), assignments numbered
+    token-major and stably sorted by expert.  Returns (indptr, token_of_row, gate_of_row,
+    row_of_flat) - the inputs of the grouped matmul's convention
+    (src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64, group_gemm_runner.cuh:161-171)."""
+    logits = np.asarray(logits, dtype=np.float32)
+    t, e = logits.shape
+    p = np.exp(logits - logits.max(axis=1, keepdims=True))
+    p = p / p.sum(axis=1, keepdims=True)
+    order = np.argsort(-p, axis=1, kind="stable")[:, :top_k]
+    flat_expert = order.reshape(-1)
+    flat_gate = np.take_along_axis(p, order, axis=1).reshape(-1).astype(np.float32)
+    perm = np.argsort(flat_expert, kind="stable")
+    indptr = np.cumsum(np.bincount(flat_expert, minlength=e)).astype(np.int64)
+    row_of_flat = np.empty(t * top_k, dtype=np.int32)
+    row_of_flat[perm] = np.arange(t * top_k, dtype=np.int32)
+    return indptr, (perm // top_k).astype(np.int32), flat_gate[perm], row_of_flat

@@ -86,6 +86,10 @@ SIGNATURES = {
     "rb200_set_launch_overlap": (_I, [_I]),
     "rb200_get_launch_overlap": (_I, []),
     "rb200_preprocess_weight": (_I, [_V, _V, _I64, _I64, _I64, _I, _I, _V]),
+    "rb200_moe_route_workspace_bytes": (ctypes.c_size_t, [_I64, _I64]),
+    "rb200_moe_route": (_I, [_V, _I64, _I64, _I64, _V, _V, _V, _V, _V, ctypes.c_size_t, _V]),
+    "rb200_moe_gather": (_I, [_V, _V, _V, _I64, _I64, _V]),
+    "rb200_moe_combine": (_I, [_V, _V, _V, _V, _I64, _I64, _I64, _V]),
     "rb200_encode_ft": (_I, [_V, _V, _V, _I64, _I64, _I, _I64, _V]),
     "rb200_unpack_zeros_autogptq": (_I, [_V, _V, _I64, _I64, _V]),
     "rb200_gemm_fp16_intx": (_I, [ctypes.POINTER(GemmDesc), _V]),

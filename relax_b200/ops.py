@@ -145,3 +145,52 @@ def encode_ft(y: torch.Tensor, weight_bits: int, group_size: int = -1):
                                            ctypes.c_void_p(scales.data_ptr()), n, k, int(weight_bits),
                                            int(group_size), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return packed, scales
+
+
+def _ptr(t):
+    import ctypes
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def moe_route(logits: torch.Tensor, top_k: int):
+    """Softmax + top-k routing (``rb200_moe_route``): returns ``(indptr int64 [E], token_of_row int32
+    [R], gate_of_row fp32 [R], row_of_flat int32 [R])`` with rows sorted by expert, the convention
+    of the grouped matmul (src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64)."""
+    import ctypes
+    from . import _lib
+    lib = _lib.load()
+    t, e = logits.shape
+    r = t * top_k
+    dev = logits.device
+    indptr = torch.empty(e, dtype=torch.int64, device=dev)
+    token_of_row = torch.empty(r, dtype=torch.int32, device=dev)
+    gate_of_row = torch.empty(r, dtype=torch.float32, device=dev)
+    row_of_flat = torch.empty(r, dtype=torch.int32, device=dev)
+    nbytes = lib.rb200_moe_route_workspace_bytes(t, top_k)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    logits = logits.contiguous().float()
+    _lib.check(lib.rb200_moe_route(_ptr(logits), t, e, top_k, _ptr(indptr), _ptr(token_of_row), _ptr(gate_of_row),
+                                   _ptr(row_of_flat), _ptr(ws), nbytes,
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return indptr, token_of_row, gate_of_row, row_of_flat
+
+
+def moe_gather(x: torch.Tensor, token_of_row: torch.Tensor) -> torch.Tensor:
+    import ctypes
+    from . import _lib
+    out = torch.empty(token_of_row.numel(), x.shape[1], dtype=torch.float16, device=x.device)
+    x = x.contiguous()
+    _lib.check(_lib.load().rb200_moe_gather(_ptr(x), _ptr(token_of_row), _ptr(out), token_of_row.numel(), x.shape[1],
+                                            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return out
+
+
+def moe_combine(y: torch.Tensor, row_of_flat: torch.Tensor, gate_of_row: torch.Tensor, top_k: int) -> torch.Tensor:
+    import ctypes
+    from . import _lib
+    tokens = row_of_flat.numel() // top_k
+    out = torch.empty(tokens, y.shape[1], dtype=torch.float16, device=y.device)
+    y = y.contiguous()
+    _lib.check(_lib.load().rb200_moe_combine(_ptr(y), _ptr(row_of_flat), _ptr(gate_of_row), _ptr(out), tokens, top_k,
+                                             y.shape[1], ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return out
