@@ -60,6 +60,8 @@ DeviceScratch* device_scratch(size_t min_partial_bytes, size_t min_counter_ints)
   s.sm_count = prop.multiProcessorCount;
   // generous defaults so ordinary use never grows: partials for 2 CTAs/SM at m <= 32
   size_t partial = (size_t)s.sm_count * 2 * 2 * 8 * 4 * 128 * sizeof(float);
+  // and for the split-k form of the prefill kernel: one 128 x 256 fp32 partial tile per SM
+  if (partial < (size_t)s.sm_count * 128 * 256 * sizeof(float)) partial = (size_t)s.sm_count * 128 * 256 * sizeof(float);
   if (partial < min_partial_bytes) partial = min_partial_bytes;
   size_t counters = 1u << 16;
   if (counters < min_counter_ints) counters = min_counter_ints;

@@ -69,11 +69,29 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
   }
 
   static const int env_grid = getenv("RB200_GEMM_GRID") ? atoi(getenv("RB200_GEMM_GRID")) : 0;
+  static const int env_split = getenv("RB200_GEMM_SPLIT_K") ? atoi(getenv("RB200_GEMM_SPLIT_K")) : 0;
   long long grid = sm_count;  // one persistent CTA per SM (a tensor-memory kernel gets occupancy 1)
   if (env_grid > 0) grid = env_grid;
+  pp.k_splits = 1;
   if (!grouped) {
-    const long long total_tiles = (long long)(p.n / kTileRows) * ((p.m + pp.nb - 1) / pp.nb);
-    if (grid > total_tiles) grid = total_tiles;
+    const long long tiles = (long long)(p.n / kTileRows) * ((p.m + pp.nb - 1) / pp.nb);
+    // fewer tiles than half the SMs: cut k so that the idle SMs take part (every split must be whole
+    // weight stages and at least 8 MMA blocks long)
+    const int kb_total = p.k / kKBlock;
+    const int blocks_per_chunk = bits == 16 ? 1 : (bits == 4 ? 4 : 2);
+    int split = (int)(sm_count / tiles);
+    if (split > 8) split = 8;
+    if (env_split > 0) split = env_split;
+    while (split > 1 && (kb_total % (split * blocks_per_chunk) != 0 || kb_total / split < 8)) --split;
+    if (split > 1 && tiles * split <= sm_count) {
+      const size_t need = (size_t)tiles * split * pp.nb * kTileRows * sizeof(float);
+      DeviceScratch* sc = device_scratch(need, (size_t)tiles * 2);
+      if (!sc) return -1;
+      pp.k_splits = split;
+      pp.partial = sc->partials;
+      pp.tickets = sc->counters;
+    }
+    if (grid > tiles * pp.k_splits) grid = tiles * pp.k_splits;
   }
   l.grid = (int)grid;
 

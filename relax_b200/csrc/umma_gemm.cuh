@@ -70,6 +70,12 @@ struct Params {
   int num_experts;
   int64_t w_expert_bytes;   // bytes between experts' packed weights
   int64_t s_expert_stride;  // elements between experts' scale (and zero) tensors
+  // split-k (ungrouped form with fewer tiles than SMs): every tile is cut into k_splits equal k
+  // ranges run by different CTAs; fp32 partial tiles meet in `partial`, the group of warps that
+  // arrives last (ticket per tile and column half) adds them in split order and stores
+  int k_splits;
+  float* partial;           // [tiles * k_splits][nb][128] fp32
+  int* tickets;             // [tiles * 2], zero at rest
 };
 
 inline size_t smem_bytes(int nb, int x_stages) {
@@ -232,6 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* e_bar = d_empty + 1;  // one per decode group: epilogue staging hand-over
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(e_bar + 2);
   TileTables& tt = *reinterpret_cast<TileTables*>(tmem_holder + 4);
+  volatile int* s_last = reinterpret_cast<volatile int*>(tmem_holder + 2);  // split-k: one flag per decode group
   __half* e_stage = reinterpret_cast<__half*>(w_ring + (size_t)kWStages * kWStageBytes);  // [2 groups][2][16][128]
 
   const int tid = threadIdx.x;
@@ -288,8 +295,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int kb_total = p.k / kKBlock;             // MMA blocks along k
   const int ft_total = p.k / kFragK;              // fragment tiles along k
   const int chunks = kDense ? kb_total : (ft_total + 3) / 4;  // weight stages per tile
-  const int total_tiles = tt.base[pp.num_experts];
+  const int S = pp.k_splits;                                   // 1 unless split-k
+  const int total_tiles = tt.base[pp.num_experts] * S;          // work items: (tile, split), split fastest
   const int ne = pp.num_experts;
+  const int kb_per = kb_total / S, ch_per = chunks / S;         // the host makes both divide
   bool ok = true;
 #ifdef RB200_ABLATE
   const int ablate = p.ablate;
@@ -312,9 +321,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     int ws = 0;
     uint32_t wph = 0;
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-      const Tile tile = get_tile(tt, ne, nb, t);
+      const Tile tile = get_tile(tt, ne, nb, t / S);
       const uint8_t* w_e = p.w + (int64_t)tile.e * pp.w_expert_bytes;
-      for (int chunk = 0; chunk < chunks; ++chunk) {
+      for (int chunk = (t % S) * ch_per; chunk < (t % S + 1) * ch_per; ++chunk) {
         if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
           ok = false;
           break;
@@ -362,7 +371,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         RB200_GTL(1, (int)tile_i);
         tc_fence_after();
-        for (int kb = 0; kb < kb_total; ++kb, ++q) {
+        const int kb_first = (t % S) * kb_per;
+        for (int kb = kb_first; kb < kb_first + kb_per; ++kb, ++q) {
           if (!um_wait(&x_full[xs], xph, p.status)) {
             ok = false;
             break;
@@ -378,14 +388,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           tc_fence_after();
-          if (kb == 0) RB200_GTL(2, (int)tile_i);
+          if (kb == kb_first) RB200_GTL(2, (int)tile_i);
           const uint32_t xbase = smem_u32(x_ring + (size_t)xs * x_stage_bytes);
           if (kDense) {
             const uint32_t wbase = smem_u32(w_ring + (size_t)ws * kWStageBytes);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               tc_mma_ss(d_col0, make_b_desc(wbase + j * 32), make_b_desc(xbase + j * 32), idesc,
-                        (kb == 0 && j == 0) ? 0u : 1u);
+                        (kb == kb_first && j == 0) ? 0u : 1u);
             tc_commit(&w_empty[ws]);
             if (++ws == kWStages) {
               ws = 0;
@@ -396,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               if (!(ablate & 8))
-                tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == 0 && j == 0) ? 0u : 1u);
+                tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == kb_first && j == 0) ? 0u : 1u);
             tc_commit(&a_empty[ab]);
           }
           tc_commit(&x_empty[xs]);
@@ -416,11 +426,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t wph = 0;
       const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const Tile tile = get_tile(tt, ne, nb, t);
+        const Tile tile = get_tile(tt, ne, nb, t / S);
         const int64_t n0 = (int64_t)tile.n_tile * kTileRows;
         const __half* s_e = p.s + (int64_t)tile.e * pp.s_expert_stride;
         const __half* z_e = p.z ? p.z + (int64_t)tile.e * pp.s_expert_stride : nullptr;
-        for (int chunk = 0; chunk < chunks; ++chunk) {
+        for (int chunk = (t % S) * ch_per; chunk < (t % S + 1) * ch_per; ++chunk) {
           if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
             ok = false;
             break;
@@ -465,8 +475,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     int xs = 0;
     uint32_t xph = 0;
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-      const int m0 = get_tile(tt, ne, nb, t).m0;
-      for (int kb = 0; kb < kb_total; ++kb) {
+      const int m0 = get_tile(tt, ne, nb, t / S).m0;
+      for (int kb = (t % S) * kb_per; kb < (t % S + 1) * kb_per; ++kb) {
         if (!mbar_wait_parked(&x_empty[xs], xph ^ 1u, p.status)) {
           ok = false;
           break;
@@ -511,7 +521,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t tile_i = 0;
     uint32_t estep = 0;  // epilogue staging steps done by this group
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
-      const Tile tile = get_tile(tt, ne, nb, t);
+      const Tile tile = get_tile(tt, ne, nb, t / S);
+      const int split = t % S;
       const int n_tile = tile.n_tile;
       const int64_t n_row = (int64_t)n_tile * kTileRows + row;
       // row index for scale / zero addressing: the expert's offset folded in (the host checks that
@@ -523,7 +534,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row_s * p.s_n]);
       }
       if (dw == 0 && lane == 0) RB200_GTL(4, (int)tile_i);
-      for (int chunk = 0; chunk < (kDense ? 0 : chunks) && ok; ++chunk) {
+      for (int chunk = split * ch_per; chunk < (kDense ? 0 : (split + 1) * ch_per) && ok; ++chunk) {
         if (!mbar_wait_parked(&w_full[ws], wph, p.status)) {
           ok = false;
           break;
@@ -590,12 +601,65 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int64_t m_end = tile.m_end;
       const int c_begin = grp * (nb / 2), c_end = c_begin + nb / 2;
       const int gj = (dw & 3) * 32 + lane;  // thread index inside the group
-      for (int c0 = c_begin; c0 < c_end; c0 += 16, ++estep) {
+      const int lrow = 32 * w4 + lane;      // TMEM lane: position of this thread's row in a partial tile
+      bool reduce_here = true;
+      if (S > 1) {
+        // publish this CTA's partial columns, then take a ticket for (tile, column half)
+        float* slot = pp.partial + ((size_t)(t / S) * S + split) * (size_t)nb * kTileRows;
+        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+          if (m0 + c0 >= m_end) break;
+          float v[16];
+          tc_ld16(lane_taddr | (d_col0 + c0), v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) slot[(size_t)(c0 + i) * kTileRows + lrow] = v[i];
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&e_bar[grp]);
+        if (!mbar_wait_parked(&e_bar[grp], estep & 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        ++estep;
+        if ((dw & 3) == 0 && lane == 0) {
+          const int prev = atomicAdd(&pp.tickets[(t / S) * 2 + grp], 1);
+          s_last[grp] = (prev == S - 1) ? 1 : 0;
+          if (prev == S - 1) pp.tickets[(t / S) * 2 + grp] = 0;  // at rest again for the next launch
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&e_bar[grp]);
+        if (!mbar_wait_parked(&e_bar[grp], estep & 1u, p.status)) {
+          ok = false;
+          break;
+        }
+        ++estep;
+        reduce_here = s_last[grp] != 0;
+        if (reduce_here) __threadfence();
+      }
+      for (int c0 = c_begin; reduce_here && c0 < c_end; c0 += 16, ++estep) {
         if (m0 + c0 >= m_end || (ablate & 4)) break;
         float v[16];
         const int es_ = (c0 - c_begin) / 16;
         if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5);
         tc_ld16(lane_taddr | (d_col0 + c0), v);
+        if (S > 1) {
+          // all splits in split order, this CTA's own part straight from tensor memory
+          float acc[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+          for (int sp = 0; sp < S; ++sp) {
+            if (sp == split) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) acc[i] += v[i];
+            } else {
+              const float* other = pp.partial + ((size_t)(t / S) * S + sp) * (size_t)nb * kTileRows;
+#pragma unroll
+              for (int i = 0; i < 16; ++i) acc[i] += __ldcg(other + (size_t)(c0 + i) * kTileRows + lrow);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = acc[i];
+        }
         if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 1);
         // transpose through shared memory: 16 batch rows x 128 weight rows of fp16 (rounded once,
         // after the epilogue), so that global stores are whole 256-byte row segments

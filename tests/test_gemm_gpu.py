@@ -30,6 +30,21 @@ def test_prefill_q4_many_tiles_per_cta(oracle):
     assert_close(got, exp)
 
 
+@pytest.mark.parametrize("m,k,n,group,asym", [(64, 4096, 128, 32, False), (100, 2048, 256, 128, True),
+                                               (300, 1024, 128, 64, False)])
+def test_prefill_split_k(oracle, m, k, n, group, asym):
+    """Fewer tiles than SMs: every tile is cut along k over several CTAs (8, 4 and 2 here); the
+    partial tiles meet in scratch and are added in split order.  Two calls in a row: the tickets
+    are back at rest after the first."""
+    case = synth.q4_case(np.random.Generator(np.random.PCG64(m + k)), m, k, n, group, asymmetric=asym)
+    rs = np.random.RandomState(m)
+    bias = rs.randn(n).astype(np.float16)
+    got, exp = _run_q4(oracle, case, bias=bias, activation="silu")
+    assert_close(got, exp, tight=False)
+    got2, _ = _run_q4(oracle, case, bias=bias, activation="silu")
+    assert np.array_equal(got, got2)
+
+
 def test_prefill_epilogues(oracle):
     rs = np.random.RandomState(11)
     m, k, n = 130, 512, 256
