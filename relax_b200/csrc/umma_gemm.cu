@@ -8,6 +8,10 @@
 
 namespace rb200 {
 
+// the split-k form is chosen automatically only once it has been validated on hardware;
+// RB200_GEMM_SPLIT_K=n forces n splits
+static constexpr bool kSplitKByDefault = false;
+
 static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count, const int64_t* indptr,
                       int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, bool grouped,
                       cudaStream_t stream) {
@@ -79,7 +83,7 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
     // weight stages and at least 8 MMA blocks long)
     const int kb_total = p.k / kKBlock;
     const int blocks_per_chunk = bits == 16 ? 1 : (bits == 4 ? 4 : 2);
-    int split = (int)(sm_count / tiles);
+    int split = kSplitKByDefault ? (int)(sm_count / tiles) : 1;
     if (split > 8) split = 8;
     if (env_split > 0) split = env_split;
     while (split > 1 && (kb_total % (split * blocks_per_chunk) != 0 || kb_total / split < 8)) --split;
