@@ -8,9 +8,8 @@
 
 namespace rb200 {
 
-// the split-k form is chosen automatically only once it has been validated on hardware;
-// RB200_GEMM_SPLIT_K=n forces n splits
-static constexpr bool kSplitKByDefault = false;
+// RB200_GEMM_SPLIT_K=n asks for n splits (1: never split)
+static constexpr bool kSplitKByDefault = true;
 
 static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count, const int64_t* indptr,
                       int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, bool grouped,
@@ -86,6 +85,7 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
     int split = kSplitKByDefault ? (int)(sm_count / tiles) : 1;
     if (split > 8) split = 8;
     if (env_split > 0) split = env_split;
+    if (split > sm_count / tiles) split = (int)(sm_count / tiles);
     while (split > 1 && (kb_total % (split * blocks_per_chunk) != 0 || kb_total / split < 8)) --split;
     if (split > 1 && tiles * split <= sm_count) {
       const size_t need = (size_t)tiles * split * pp.nb * kTileRows * sizeof(float);

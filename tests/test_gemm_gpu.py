@@ -34,7 +34,6 @@ def test_prefill_q4_many_tiles_per_cta(oracle):
 
 @pytest.mark.parametrize("m,k,n,group,asym", [(64, 4096, 128, 32, False), (100, 2048, 256, 128, True),
                                                (300, 1024, 128, 64, False)])
-@pytest.mark.skipif(os.environ.get("RB200_GEMM_SPLIT_K", "") == "", reason="split-k is opt-in: RB200_GEMM_SPLIT_K=8")
 def test_prefill_split_k(oracle, m, k, n, group, asym):
     """Fewer tiles than SMs: every tile is cut along k over several CTAs (8, 4 and 2 here); the
     partial tiles meet in scratch and are added in split order.  Two calls in a row: the tickets
