@@ -207,7 +207,9 @@ __device__ __forceinline__ void decode_any(int kbm, const GemvParams& p, const u
   }
 }
 
-template <int BITS, int ZMODE, int GROUP, int SRC>
+// SPLITK: compiled separately so that the unsplit kernel carries none of the reduction code
+// (with it, its epilogue was about 1 us per tile slower).
+template <int BITS, int ZMODE, int GROUP, int SRC, bool SPLITK>
 __global__ void __launch_bounds__(kThreads, 1)
     umma_gemm_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_x,
                      const __grid_constant__ CUtensorMap tmap_w) {
@@ -295,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int kb_total = p.k / kKBlock;             // MMA blocks along k
   const int ft_total = p.k / kFragK;              // fragment tiles along k
   const int chunks = kDense ? kb_total : (ft_total + 3) / 4;  // weight stages per tile
-  const int S = pp.k_splits;                                   // 1 unless split-k
+  const int S = SPLITK ? pp.k_splits : 1;                      // 1 unless split-k
   const int total_tiles = tt.base[pp.num_experts] * S;          // work items: (tile, split), split fastest
   const int ne = pp.num_experts;
   const int kb_per = kb_total / S, ch_per = chunks / S;         // the host makes both divide
@@ -603,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int gj = (dw & 3) * 32 + lane;  // thread index inside the group
       const int lrow = 32 * w4 + lane;      // TMEM lane: position of this thread's row in a partial tile
       bool reduce_here = true;
-      if (S > 1) {
+      if (SPLITK && S > 1) {
         // publish this CTA's partial columns, then take a ticket for (tile, column half)
         float* slot = pp.partial + ((size_t)(t / S) * S + split) * (size_t)nb * kTileRows;
         for (int c0 = c_begin; c0 < c_end; c0 += 16) {
@@ -642,7 +644,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int es_ = (c0 - c_begin) / 16;
         if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5);
         tc_ld16(lane_taddr | (d_col0 + c0), v);
-        if (S > 1) {
+        if (SPLITK && S > 1) {
           // all splits in split order, this CTA's own part straight from tensor memory
           float acc[16];
 #pragma unroll

@@ -5,9 +5,9 @@
 namespace rb200 {
 namespace um {
 
-template <int BITS, int ZMODE, int GROUP, int SRC>
-int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& tw, cudaStream_t stream) {
-  auto kern = umma_gemm_kernel<BITS, ZMODE, GROUP, SRC>;
+template <int BITS, int ZMODE, int GROUP, int SRC, bool SPLITK>
+int launch_inst2(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& tw, cudaStream_t stream) {
+  auto kern = umma_gemm_kernel<BITS, ZMODE, GROUP, SRC, SPLITK>;
   static thread_local int configured_device = -1;
   int dev = 0;
   RB200_CUDA(cudaGetDevice(&dev));
@@ -18,6 +18,12 @@ int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, const 
   kern<<<l.grid, kThreads, l.smem, stream>>>(pp, tx, tw);
   RB200_CUDA(cudaGetLastError());
   return 0;
+}
+
+template <int BITS, int ZMODE, int GROUP, int SRC>
+int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& tw, cudaStream_t stream) {
+  if (pp.k_splits > 1) return launch_inst2<BITS, ZMODE, GROUP, SRC, true>(pp, l, tx, tw, stream);
+  return launch_inst2<BITS, ZMODE, GROUP, SRC, false>(pp, l, tx, tw, stream);
 }
 
 template <int BITS, int ZMODE>
