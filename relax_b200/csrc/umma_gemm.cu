@@ -78,15 +78,15 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
   pp.k_splits = 1;
   if (!grouped) {
     const long long tiles = (long long)(p.n / kTileRows) * ((p.m + pp.nb - 1) / pp.nb);
-    // fewer tiles than half the SMs: cut k so that the idle SMs take part (every split must be whole
-    // weight stages and at least 8 MMA blocks long)
+    // fewer tiles than half the SMs: cut k, in whole weight stages, so that the idle SMs take part
     const int kb_total = p.k / kKBlock;
     const int blocks_per_chunk = bits == 16 ? 1 : (bits == 4 ? 4 : 2);
     int split = kSplitKByDefault ? (int)(sm_count / tiles) : 1;
     if (split > 8) split = 8;
     if (env_split > 0) split = env_split;
     if (split > sm_count / tiles) split = (int)(sm_count / tiles);
-    while (split > 1 && (kb_total % (split * blocks_per_chunk) != 0 || kb_total / split < 8)) --split;
+    const int chunks = (kb_total + blocks_per_chunk - 1) / blocks_per_chunk;
+    while (split > 1 && chunks / split * blocks_per_chunk < 8) --split;  // every split at least 8 MMA blocks
     if (split > 1 && tiles * split <= sm_count) {
       const size_t need = (size_t)tiles * split * pp.nb * kTileRows * sizeof(float);
       DeviceScratch* sc = device_scratch(need, (size_t)tiles * 2);

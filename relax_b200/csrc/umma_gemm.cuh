@@ -300,7 +300,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int S = SPLITK ? pp.k_splits : 1;                      // 1 unless split-k
   const int total_tiles = tt.base[pp.num_experts] * S;          // work items: (tile, split), split fastest
   const int ne = pp.num_experts;
-  const int kb_per = kb_total / S, ch_per = chunks / S;         // the host makes both divide
+  // split sp covers the weight stages [sp * chunks / S, (sp + 1) * chunks / S) and their MMA blocks
+  auto ch_lo = [&](int sp) { return (int)((long long)sp * chunks / S); };
+  auto kb_lo = [&](int sp) { return min(ch_lo(sp) * kBlocksPerChunk, kb_total); };
   bool ok = true;
 #ifdef RB200_ABLATE
   const int ablate = p.ablate;
@@ -325,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
       const Tile tile = get_tile(tt, ne, nb, t / S);
       const uint8_t* w_e = p.w + (int64_t)tile.e * pp.w_expert_bytes;
-      for (int chunk = (t % S) * ch_per; chunk < (t % S + 1) * ch_per; ++chunk) {
+      for (int chunk = ch_lo(t % S); chunk < ch_lo(t % S + 1); ++chunk) {
         if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
           ok = false;
           break;
@@ -373,8 +375,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         RB200_GTL(1, (int)tile_i);
         tc_fence_after();
-        const int kb_first = (t % S) * kb_per;
-        for (int kb = kb_first; kb < kb_first + kb_per; ++kb, ++q) {
+        const int kb_first = kb_lo(t % S), kb_end = kb_lo(t % S + 1);
+        for (int kb = kb_first; kb < kb_end; ++kb, ++q) {
           if (!um_wait(&x_full[xs], xph, p.status)) {
             ok = false;
             break;
@@ -432,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int64_t n0 = (int64_t)tile.n_tile * kTileRows;
         const __half* s_e = p.s + (int64_t)tile.e * pp.s_expert_stride;
         const __half* z_e = p.z ? p.z + (int64_t)tile.e * pp.s_expert_stride : nullptr;
-        for (int chunk = (t % S) * ch_per; chunk < (t % S + 1) * ch_per; ++chunk) {
+        for (int chunk = ch_lo(t % S); chunk < ch_lo(t % S + 1); ++chunk) {
           if (!mbar_wait_parked(&w_empty[ws], wph ^ 1u, p.status)) {
             ok = false;
             break;
@@ -478,7 +480,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t xph = 0;
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
       const int m0 = get_tile(tt, ne, nb, t / S).m0;
-      for (int kb = (t % S) * kb_per; kb < (t % S + 1) * kb_per; ++kb) {
+      for (int kb = kb_lo(t % S); kb < kb_lo(t % S + 1); ++kb) {
         if (!mbar_wait_parked(&x_empty[xs], xph ^ 1u, p.status)) {
           ok = false;
           break;
@@ -536,7 +538,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row_s * p.s_n]);
       }
       if (dw == 0 && lane == 0) RB200_GTL(4, (int)tile_i);
-      for (int chunk = split * ch_per; chunk < (kDense ? 0 : (split + 1) * ch_per) && ok; ++chunk) {
+      for (int chunk = ch_lo(split); chunk < (kDense ? 0 : ch_lo(split + 1)) && ok; ++chunk) {
         if (!mbar_wait_parked(&w_full[ws], wph, p.status)) {
           ok = false;
           break;

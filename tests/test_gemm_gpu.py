@@ -33,11 +33,12 @@ def test_prefill_q4_many_tiles_per_cta(oracle):
 
 
 @pytest.mark.parametrize("m,k,n,group,asym", [(64, 4096, 128, 32, False), (100, 2048, 256, 128, True),
-                                               (300, 1024, 128, 64, False)])
+                                               (300, 1024, 128, 64, False), (100, 1088, 128, 32, False),
+                                               (64, 2752, 256, 32, True)])
 def test_prefill_split_k(oracle, m, k, n, group, asym):
-    """Fewer tiles than SMs: every tile is cut along k over several CTAs (8, 4 and 2 here); the
-    partial tiles meet in scratch and are added in split order.  Two calls in a row: the tickets
-    are back at rest after the first."""
+    """Fewer tiles than SMs: every tile is cut along k over several CTAs (8, 4, 2 and - with a
+    ragged last weight stage - 2 and 5 unequal ranges here); the partial tiles meet in scratch and
+    are added in split order.  Two calls in a row: the tickets are back at rest after the first."""
     case = synth.q4_case(np.random.Generator(np.random.PCG64(m + k)), m, k, n, group, asymmetric=asym)
     rs = np.random.RandomState(m)
     bias = rs.randn(n).astype(np.float16)
