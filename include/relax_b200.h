@@ -60,6 +60,8 @@ RB200_API int rb200_get_launch_overlap(void);
 /* Source layouts accepted by rb200_preprocess_weight. */
 #define RB200_LAYOUT_FT_KN 0 /* int8 container [K, N/2] (int4, low nibble = even column) or [K, N] (int8), signed codes */
 #define RB200_LAYOUT_Q4_NK 1 /* uint32 [N, K/8], nibble j of a word = element 8*word + j, unsigned codes */
+#define RB200_LAYOUT_GATE_UP_INTERLEAVE 0x100 /* flag, OR-ed into a layout: fragment row block nb = gate rows 8nb..8nb+7
+                                                 followed by up rows 8nb..8nb+7 (source rows [0, n/2) = gate, [n/2, n) = up) */
 #define RB200_LAYOUT_AUTOGPTQ_KN 2 /* uint32 [K/8, N], nibble j of word (k/8, n) = element k = 8*(k/8) + j, unsigned
                                       codes (tests/python/dlight/test_gpu_gemv.py:639-649) */
 
@@ -93,6 +95,12 @@ RB200_API int rb200_unpack_zeros_autogptq(const void* zq, void* zeros_out, int64
 #define RB200_ACT_RELU 1
 #define RB200_ACT_SILU 2
 #define RB200_ACT_GELU 3
+/* Fused gated MLP: the weight holds gate rows [0, n/2) and up rows [n/2, n) and was repacked with
+ * RB200_LAYOUT_GATE_UP_INTERLEAVE (scales / zeros permuted with rb200_interleave_gate_up); the
+ * output is fp16 [m, n/2] = silu(x @ gate^T) * (x @ up^T), both factors taken from the fp32
+ * accumulators (the m > 32 kernel rounds them to fp16 first).  No bias / residual / unary op.
+ * The reference leaves this to a separate split + silu + multiply after the matmul. */
+#define RB200_ACT_SWIGLU 4
 #define RB200_BIN_NONE 0
 #define RB200_BIN_PLUS 1
 #define RB200_BIN_MULTIPLY 2
@@ -240,6 +248,13 @@ RB200_API int rb200_moe_gather(const void* x, const int32_t* token_of_row, void*
                                void* stream);
 RB200_API int rb200_moe_combine(const void* y, const int32_t* row_of_flat, const float* gate_of_row, void* out,
                                 int64_t tokens, int64_t top_k, int64_t n, void* stream);
+
+/*
+ * The row permutation of RB200_LAYOUT_GATE_UP_INTERLEAVE applied to an fp16 tensor viewed as
+ * [outer][n][inner] (scales / zero points: [n, k/g] -> outer 1, inner k/g; [k/g, n] -> outer k/g,
+ * inner 1; [n] -> outer 1, inner 1):  dst[o][16b + r][i] = src[o][r < 8 ? 8b + r : n/2 + 8b + r - 8][i].
+ */
+RB200_API int rb200_interleave_gate_up(const void* src, void* dst, int64_t outer, int64_t n, int64_t inner, void* stream);
 
 /* ------------------------------------------------------------------ quantiser */
 

@@ -99,6 +99,9 @@ RB200_API int RB200FuncListGlobalNames(int* out_size, const char*** out_array);
  *      the decode + matmul of test_gpu_gemv.py:193-206 with fp32 accumulation.
  *  "relax_b200.dequantize"(w_pre, scales, zeros|null, layout:int, weight_bits:int, group_size:int,
  *       zero_const:float, out fp16 [N, K])        verification aid.
+ *  "relax_b200.preprocess_weight_gate_up"(packed_weight, layout:int, is_int4:int, out)   repack with the
+ *      gate/up row interleave; "relax_b200.interleave_gate_up"(f16 tensor, n_axis:int, out) permutes
+ *      scales / zeros alike; activation "swiglu" of the matmul entries then writes silu(gate) * up.
  *  "relax_b200.preprocess_weight_autogptq"(qweight u32 [K/8, N], out)   AutoGPTQ source layout
  *  "relax_b200.unpack_zeros_autogptq"(qzeros u32 [G, N/8], out f16 [G, N])   f16(zq) + 1
  *  "relax_b200.gemm_fp16_autogptq"(x, w_pre, scales f16 [G, N], zeros f16 [G, N], bias|null, out)

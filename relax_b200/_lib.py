@@ -90,6 +90,7 @@ SIGNATURES = {
     "rb200_moe_route": (_I, [_V, _I64, _I64, _I64, _V, _V, _V, _V, _V, ctypes.c_size_t, _V]),
     "rb200_moe_gather": (_I, [_V, _V, _V, _I64, _I64, _V]),
     "rb200_moe_combine": (_I, [_V, _V, _V, _V, _I64, _I64, _I64, _V]),
+    "rb200_interleave_gate_up": (_I, [_V, _V, _I64, _I64, _I64, _V]),
     "rb200_encode_ft": (_I, [_V, _V, _V, _I64, _I64, _I, _I64, _V]),
     "rb200_unpack_zeros_autogptq": (_I, [_V, _V, _I64, _I64, _V]),
     "rb200_gemm_fp16_intx": (_I, [ctypes.POINTER(GemmDesc), _V]),

@@ -145,6 +145,7 @@ int parse_act(const char* s, int* out) {
   if (!strcmp(s, "relu")) return *out = RB200_ACT_RELU, 0;
   if (!strcmp(s, "silu")) return *out = RB200_ACT_SILU, 0;
   if (!strcmp(s, "gelu")) return *out = RB200_ACT_GELU, 0;
+  if (!strcmp(s, "swiglu")) return *out = RB200_ACT_SWIGLU, 0;
   set_last_error("unknown activation '%s'", s);
   return -1;
 }
@@ -253,9 +254,12 @@ int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int
   RB200_CHECK(n > 0 && k > 0 && n % 16 == 0 && k % frag == 0,
               "preprocess needs n %% 16 == 0 and k %% %d == 0 (n=%lld, k=%lld)", frag, (long long)n,
               (long long)k);
-  RB200_CHECK(src_layout == RB200_LAYOUT_FT_KN ||
-                  ((src_layout == RB200_LAYOUT_Q4_NK || src_layout == RB200_LAYOUT_AUTOGPTQ_KN) && is_int4),
+  const int base_layout = src_layout & ~RB200_LAYOUT_GATE_UP_INTERLEAVE;
+  RB200_CHECK(base_layout == RB200_LAYOUT_FT_KN ||
+                  ((base_layout == RB200_LAYOUT_Q4_NK || base_layout == RB200_LAYOUT_AUTOGPTQ_KN) && is_int4),
               "unsupported source layout %d for %d-bit weights", src_layout, bits);
+  RB200_CHECK(!(src_layout & RB200_LAYOUT_GATE_UP_INTERLEAVE) || n % 32 == 0,
+              "the gate/up interleave needs n %% 32 == 0 (n=%lld)", (long long)n);
   RB200_CHECK(aligned16(dst), "dst must be 16-byte aligned");
   return preprocess_launch(src, dst, num_experts, k, n, bits, src_layout,
                            static_cast<cudaStream_t>(stream));
@@ -266,6 +270,13 @@ int rb200_unpack_zeros_autogptq(const void* zq, void* zeros_out, int64_t groups,
   RB200_CHECK(groups >= 1 && n >= 8 && n % 8 == 0, "need groups >= 1 and n %% 8 == 0 (groups=%lld, n=%lld)",
               (long long)groups, (long long)n);
   return unpack_zeros_autogptq_launch(zq, zeros_out, groups, n, static_cast<cudaStream_t>(stream));
+}
+
+int rb200_interleave_gate_up(const void* src, void* dst, int64_t outer, int64_t n, int64_t inner, void* stream) {
+  RB200_CHECK(src && dst && src != dst, "src and dst must be distinct non-NULL tensors");
+  RB200_CHECK(outer >= 1 && inner >= 1 && n > 0 && n % 32 == 0, "need outer, inner >= 1 and n %% 32 == 0 (n=%lld)",
+              (long long)n);
+  return interleave_rows_launch(src, dst, outer, n, inner, static_cast<cudaStream_t>(stream));
 }
 
 size_t rb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int weight_bits) {
@@ -284,9 +295,15 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
   if (d->m == 0) return 0;  // empty batch: nothing to launch (pointers of empty tensors may be NULL)
   RB200_CHECK(d->x && d->out, "x and out must be non-NULL");
   const int64_t ldx = d->ldx > 0 ? d->ldx : d->k;
-  const int64_t ldo = d->ldo > 0 ? d->ldo : d->n;
+  const bool swiglu = d->activation == RB200_ACT_SWIGLU;
+  const int64_t ldo = d->ldo > 0 ? d->ldo : (swiglu ? d->n / 2 : d->n);
   RB200_CHECK(aligned16(d->x) && ldx % 8 == 0, "x must be 16-byte aligned with ldx %% 8 == 0");
   RB200_CHECK(d->binary_op == RB200_BIN_NONE || d->residual, "binary_op needs a residual tensor");
+  if (swiglu) {
+    RB200_CHECK(!d->bias && d->binary_op == RB200_BIN_NONE && d->unary_op == RB200_UN_IDENTITY && !d->workspace,
+                "the fused gate/up activation takes no bias, residual, unary op or caller workspace");
+    RB200_CHECK(d->n % 32 == 0, "the fused gate/up activation needs n %% 32 == 0");
+  }
   RB200_CHECK(d->bias_stride == 0 || d->bias_stride == d->n, "bias_stride must be 0 or n");
 
   Epilogue epi;
@@ -300,7 +317,7 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
   const int group = (d->group_size <= 0 || d->group_size >= d->k) ? 0 : (int)d->group_size;
 
   static const bool force_scratch_path = getenv("RB200_GEMV_SCRATCH_PATH") != nullptr;
-  if (d->m <= 32 && !d->workspace && !force_scratch_path) {
+  if (d->m <= 32 && !d->workspace && (!force_scratch_path || swiglu)) {
     // default decode path: cluster split-k, no global scratch beyond the status word
     DeviceScratch* sc = device_scratch(0, 0);
     if (!sc) return -1;
@@ -342,6 +359,7 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
       int which = 0;
       if (p.n <= 4096) which = 2;
       if (forced >= 0) which = forced;
+      if (swiglu && which == 1) which = 0;  // the comparison kernel has no fused gate/up epilogue
       if (which == 0)
         return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
                            kFlagCount, epoch, stream);

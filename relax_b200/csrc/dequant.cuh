@@ -173,6 +173,9 @@ __device__ __forceinline__ void decode_int8_pair(uint32_t w_g, uint32_t w_g8, co
 }
 
 // ---------------------------------------------------------------- epilogue
+constexpr int kActSwiglu = 4;  // fused gated MLP: out = silu(gate) * up, see RB200_ACT_SWIGLU
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + __expf(-gate)) * up; }
+
 __device__ __forceinline__ float apply_act(float v, int act) {
   switch (act) {
     case 1:

@@ -455,6 +455,17 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     if (store && active) {
       griddep_wait();  // the previous kernel may still read what this store overwrites
+      if (p.epi.act == kActSwiglu) {
+        const int64_t f = (int64_t)blk * 8 + g;  // rows g / g+8 are gate_f / up_f (interleaved repack)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int64_t m = mt * 8 + t * 2 + cc;
+            if (m < p.m) p.out[m * p.ldo + f] = __float2half_rn(silu_mul(acc[mt][0][cc], acc[mt][0][cc + 2]));
+          }
+        continue;
+      }
       const int64_t n0 = (int64_t)blk * 16 + g;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {

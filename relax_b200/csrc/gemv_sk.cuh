@@ -339,6 +339,18 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
   auto store_tile = [&](const float (&v)[MT][4], int tile_i) {
     const int blk = tile_i * kConsumerWarps + warp;
     if (blk >= n_blocks) return;
+    if (p.epi.act == kActSwiglu) {
+      // rows g / g+8 of the block are gate_f / up_f of f = 8 blk + g (interleaved repack)
+      const int64_t f = (int64_t)blk * 8 + g;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int64_t m = mt * 8 + t * 2 + cc;
+          if (m < p.m) p.out[m * p.ldo + f] = __float2half_rn(silu_mul(v[mt][cc], v[mt][cc + 2]));
+        }
+      return;
+    }
     const int64_t n0 = (int64_t)blk * 16 + g;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)

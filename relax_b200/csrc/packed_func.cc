@@ -138,12 +138,13 @@ int preprocess_common(const char* fn, const DLTensor* w, const DLTensor* out, bo
   const int64_t cols = w->shape[is_2d ? 1 : 2];
   const int64_t elem_bytes = w->dtype.bits / 8;
   int64_t k, n;
-  if (layout == RB200_LAYOUT_FT_KN) {
+  const int base_layout = layout & 0xff;  // without the gate/up interleave flag
+  if (base_layout == RB200_LAYOUT_FT_KN) {
     PF_CHECK(w->dtype.bits == 8 && (w->dtype.code == kDLInt || w->dtype.code == kDLUInt),
              "%s: FT weights must be int8", fn);
     k = rows;
     n = cols * (is_int4 ? 2 : 1);
-  } else if (layout == RB200_LAYOUT_AUTOGPTQ_KN) {
+  } else if (base_layout == RB200_LAYOUT_AUTOGPTQ_KN) {
     PF_CHECK(is_dtype(w, kDLUInt, 32) || is_dtype(w, kDLInt, 32), "%s: AutoGPTQ weights must be uint32 [K/8, N]", fn);
     k = rows * 8;
     n = cols;
@@ -228,12 +229,39 @@ int pf_unpack_zeros_autogptq(RB200Value* v, int* tc, int n, RB200Value* ret, int
   return rb200_unpack_zeros_autogptq(data_of(zq), data_of(out), zq->shape[0], out->shape[1], rb200_get_stream());
 }
 
+// (packed_weight, layout:int (RB200_LAYOUT_*), is_int4:int, out): repack with the gate/up row interleave
+int pf_preprocess_gate_up(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "relax_b200.preprocess_weight_gate_up"};
+  const DLTensor *w, *out;
+  int64_t layout, is_int4;
+  PF_CHECK(n == 4, "%s expects (packed_weight, layout, is_int4, out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &w) || a.integer(1, &layout) || a.integer(2, &is_int4) || a.tensor(3, &out)) return -1;
+  PF_CHECK(layout == RB200_LAYOUT_FT_KN || layout == RB200_LAYOUT_Q4_NK, "%s: layout must be FT_KN or Q4_NK", a.fname);
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return preprocess_common(a.fname, w, out, is_int4 != 0, (int)layout | RB200_LAYOUT_GATE_UP_INTERLEAVE);
+}
+// (src f16, n_axis:int, out f16): the same row permutation for scales / zero points along axis n_axis
+int pf_interleave_gate_up(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "relax_b200.interleave_gate_up"};
+  const DLTensor *src, *out;
+  int64_t axis;
+  PF_CHECK(n == 3, "%s expects (tensor, n_axis, out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &src) || a.integer(1, &axis) || a.tensor(2, &out)) return -1;
+  if (check_tensor(a.fname, "tensor", src, kDLFloat, 16) || check_tensor(a.fname, "out", out, kDLFloat, 16)) return -1;
+  PF_CHECK(axis >= 0 && axis < src->ndim && numel(src) == numel(out), "%s: bad axis or out size", a.fname);
+  int64_t outer = 1, inner = 1;
+  for (int i = 0; i < axis; ++i) outer *= src->shape[i];
+  for (int i = (int)axis + 1; i < src->ndim; ++i) inner *= src->shape[i];
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_interleave_gate_up(data_of(src), data_of(out), outer, src->shape[axis], inner, rb200_get_stream());
+}
+
 // ------------------------------------------------------------------ GEMM shims
 int parse_names(const char* fn, const char* act, const char* bin, const char* un, rb200_gemm_desc* d) {
   struct {
     const char* s;
     int v;
-  } acts[] = {{"", 0}, {"identity", 0}, {"relu", 1}, {"silu", 2}, {"gelu", 3}},
+  } acts[] = {{"", 0}, {"identity", 0}, {"relu", 1}, {"silu", 2}, {"gelu", 3}, {"swiglu", 4}},
     bins[] = {{"", 0}, {"none", 0}, {"plus", 1}, {"multiply", 2}},
     uns[] = {{"", 0}, {"identity", 0}, {"relu", 1}};
   bool ok = false;
@@ -340,8 +368,9 @@ int pf_gemm_q4f16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, 
   PF_CHECK(x->ndim >= 1 && x->shape[x->ndim - 1] == k, "%s: x inner extent %lld != k=%lld", fname,
            (long long)x->shape[x->ndim - 1], (long long)k);
   const int64_t m = lead_rows(x);
-  PF_CHECK(numel(out) == m * n, "%s: out has %lld elements, expected %lld", fname,
-           (long long)numel(out), (long long)(m * n));
+  const int64_t n_out = !strcmp(act, "swiglu") ? n / 2 : n;  // the fused gate/up form halves the width
+  PF_CHECK(numel(out) == m * n_out, "%s: out has %lld elements, expected %lld", fname,
+           (long long)numel(out), (long long)(m * n_out));
   PF_CHECK(group > 0 && k % group == 0, "%s: group_size=%lld must divide k=%lld", fname,
            (long long)group, (long long)k);
   PF_CHECK(numel(s) == n * (k / group), "%s: scales must be [N, K/group]", fname);
@@ -375,7 +404,7 @@ int pf_gemm_q4f16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, 
   d.n = n;
   d.k = k;
   d.ldx = k;
-  d.ldo = n;
+  d.ldo = n_out;
   d.group_size = group;
   d.scale_stride_n = k / group;
   d.scale_stride_g = 1;
@@ -620,6 +649,8 @@ void ensure_builtins() {
   done = true;
   register_builtin("cutlass.ft_preprocess_weight", pf_ft_preprocess_weight);
   register_builtin("relax_b200.preprocess_weight_q4f16", pf_preprocess_q4f16);
+  register_builtin("relax_b200.preprocess_weight_gate_up", pf_preprocess_gate_up);
+  register_builtin("relax_b200.interleave_gate_up", pf_interleave_gate_up);
   register_builtin("relax_b200.preprocess_weight_autogptq", pf_preprocess_autogptq);
   register_builtin("relax_b200.unpack_zeros_autogptq", pf_unpack_zeros_autogptq);
   register_builtin("relax_b200.gemm_fp16_autogptq", pf_gemm_autogptq);

@@ -40,9 +40,17 @@ __global__ void unpack_zeros_autogptq_kernel(const uint32_t* __restrict__ zq, __
   }
 }
 
+// Gate/up interleave: the source holds gate rows [0, N/2) and up rows [N/2, N); fragment row block
+// nb then takes gate rows 8nb..8nb+7 as its rows 0..7 and up rows 8nb..8nb+7 as its rows 8..15, so
+// that one lane of the warp-MMA kernels (rows g and g+8) owns gate_f and up_f of the same f.
+__host__ __device__ __forceinline__ int64_t gate_up_source_row(int64_t j, int64_t N) {
+  const int64_t nb = j >> 4, r = j & 15;
+  return r < 8 ? 8 * nb + r : N / 2 + 8 * nb + (r - 8);
+}
+
 template <int BITS, int LAYOUT>
 __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
-                              int64_t K, int64_t N, int64_t units_per_expert, int64_t total_units) {
+                              int64_t K, int64_t N, int64_t units_per_expert, int64_t total_units, int interleave) {
   constexpr int kFrag = BITS == 4 ? 64 : 32;
   const int64_t expert_bytes = K * N * BITS / 8;
   for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total_units;
@@ -66,7 +74,9 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
         uint32_t w = 0;
 #pragma unroll
         for (int p = 0; p < 8; ++p) {
-          uint32_t c = load_code<BITS, LAYOUT>(s, nb * 16 + g + row_of[p], k0 + 4 * j + k_of[p], K, N);
+          int64_t srow = nb * 16 + g + row_of[p];
+          if (interleave) srow = gate_up_source_row(srow, N);
+          uint32_t c = load_code<BITS, LAYOUT>(s, srow, k0 + 4 * j + k_of[p], K, N);
           w |= c << (4 * p);
         }
         words[j] = w;
@@ -79,8 +89,11 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
         for (int r8 = 0; r8 < 2; ++r8) {
           uint32_t w = 0;
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4)
-            w |= load_code<BITS, LAYOUT>(s, nb * 16 + g + 8 * r8, k0 + 4 * j + c4, K, N) << (8 * c4);
+          for (int c4 = 0; c4 < 4; ++c4) {
+            int64_t srow = nb * 16 + g + 8 * r8;
+            if (interleave) srow = gate_up_source_row(srow, N);
+            w |= load_code<BITS, LAYOUT>(s, srow, k0 + 4 * j + c4, K, N) << (8 * c4);
+          }
           words[2 * j + r8] = w;
         }
     }
@@ -90,8 +103,21 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
 
 }  // namespace
 
+// dst[o][j][i] = src[o][gate_up_source_row(j)][i] over fp16 elements: the row permutation of the
+// interleaved repack applied to a scale / zero-point tensor viewed as [outer][n][inner]
+__global__ void interleave_rows_kernel(const __half* __restrict__ src, __half* __restrict__ dst, int64_t outer,
+                                       int64_t N, int64_t inner) {
+  const int64_t total = outer * N * inner;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t in = i % inner, j = (i / inner) % N, o = i / (inner * N);
+    dst[i] = src[(o * N + gate_up_source_row(j, N)) * inner + in];
+  }
+}
+
 int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, int64_t n, int bits,
-                      int layout, cudaStream_t stream) {
+                      int layout_flags, cudaStream_t stream) {
+  const int interleave = (layout_flags & 0x100) ? 1 : 0;
+  const int layout = layout_flags & 0xff;
   const int64_t units = k * n * bits / 8 / 16;
   const int64_t total = units * experts;
   const int threads = 256;
@@ -101,15 +127,26 @@ int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, in
   const uint8_t* s = static_cast<const uint8_t*>(src);
   uint8_t* d = static_cast<uint8_t*>(dst);
   if (bits == 4 && layout == 0)
-    repack_kernel<4, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+    repack_kernel<4, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
   else if (bits == 4 && layout == 1)
-    repack_kernel<4, 1><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+    repack_kernel<4, 1><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
   else if (bits == 4 && layout == 2)
-    repack_kernel<4, 2><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+    repack_kernel<4, 2><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
   else if (bits == 8 && layout == 0)
-    repack_kernel<8, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total);
+    repack_kernel<8, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
   else
     RB200_CHECK(false, "unsupported preprocess combination bits=%d layout=%d", bits, layout);
+  RB200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int interleave_rows_launch(const void* src, void* dst, int64_t outer, int64_t n, int64_t inner, cudaStream_t stream) {
+  const int64_t total = outer * n * inner;
+  if (total == 0) return 0;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  interleave_rows_kernel<<<(int)blocks, 256, 0, stream>>>(static_cast<const __half*>(src), static_cast<__half*>(dst),
+                                                         outer, n, inner);
   RB200_CUDA(cudaGetLastError());
   return 0;
 }

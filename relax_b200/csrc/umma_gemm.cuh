@@ -683,9 +683,27 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int pass = 0; pass < 2; ++pass) {
           const int mi = pass * 8 + (gj >> 4), ch = gj & 15;
           const int64_t m = m0 + c0 + mi;
-          if (m < m_end)
+          if (p.epi.act == kActSwiglu) {
+            // interleaved repack: 16-byte chunk 2q of a staged row holds gate_f, chunk 2q+1 up_f for
+            // the same eight f; the even-chunk threads combine them and store 16 bytes of [m, n/2]
+            if (m < m_end && (ch & 1) == 0) {
+              const uint4 gv = *reinterpret_cast<const uint4*>(st + mi * kTileRows + ch * 8);
+              const uint4 uv = *reinterpret_cast<const uint4*>(st + mi * kTileRows + ch * 8 + 8);
+              const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+              const __half2* uh = reinterpret_cast<const __half2*>(&uv);
+              __half2 res[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float2 gf = __half22float2(gh[q]), uf = __half22float2(uh[q]);
+                res[q] = __floats2half2_rn(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
+              }
+              *reinterpret_cast<uint4*>(p.out + m * p.ldo + (int64_t)n_tile * (kTileRows / 2) + (ch >> 1) * 8) =
+                  *reinterpret_cast<const uint4*>(res);
+            }
+          } else if (m < m_end) {
             *reinterpret_cast<uint4*>(p.out + m * p.ldo + (int64_t)n_tile * kTileRows + ch * 8) =
                 *reinterpret_cast<const uint4*>(st + mi * kTileRows + ch * 8);
+          }
         }
         if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 4);
       }

@@ -49,7 +49,7 @@ def gemm_fp16_q4f16(x, w_pre, scales, zeros=None, bias=None, residual=None,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode + matmul for q4f16_1-layout weights (tests/python/dlight/test_gpu_gemv.py:193-206),
     fp32 accumulation, fp16 output."""
-    n = w_pre.shape[0]
+    n = w_pre.shape[0] // (2 if activation == "swiglu" else 1)
     if out is None:
         out = torch.empty(*x.shape[:-1], n, dtype=torch.float16, device=x.device)
     get_global_func("relax_b200.gemm_fp16_q4f16")(x, w_pre, scales, zeros, bias, residual, activation,
@@ -193,4 +193,18 @@ def moe_combine(y: torch.Tensor, row_of_flat: torch.Tensor, gate_of_row: torch.T
     y = y.contiguous()
     _lib.check(_lib.load().rb200_moe_combine(_ptr(y), _ptr(row_of_flat), _ptr(gate_of_row), _ptr(out), tokens, top_k,
                                              y.shape[1], ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return out
+
+
+def preprocess_weight_gate_up(packed_weight: torch.Tensor, layout: int = LAYOUT_Q4_NK, is_int4: bool = True) -> torch.Tensor:
+    """Repack a fused gate/up weight (gate rows [0, N/2), up rows [N/2, N)) with the row interleave
+    the ``activation="swiglu"`` epilogue expects; scales and zero points need the same permutation
+    (:func:`interleave_gate_up`)."""
+    return get_global_func("relax_b200.preprocess_weight_gate_up")(packed_weight, int(layout), bool(is_int4))
+
+
+def interleave_gate_up(t: torch.Tensor, n_axis: int = 0) -> torch.Tensor:
+    """The gate/up row permutation applied to an fp16 scale / zero-point tensor along ``n_axis``."""
+    out = torch.empty_like(t)
+    get_global_func("relax_b200.interleave_gate_up")(t.contiguous(), int(n_axis), out)
     return out

@@ -152,7 +152,7 @@ def _wrap_preprocess(pf: PackedFunc) -> Callable:
 
 
 _ALLOCATING = {"cutlass.ft_preprocess_weight", "relax_b200.preprocess_weight_q4f16",
-               "relax_b200.preprocess_weight_autogptq"}
+               "relax_b200.preprocess_weight_autogptq", "relax_b200.preprocess_weight_gate_up"}
 _CACHE = {}
 
 
