@@ -397,6 +397,59 @@ def run_gpu(args):
                    "l2": "x + packed weight + out = 152 MB per launch, larger than L2"}
         del pw, ps, pz, px, po
 
+    # ---- further secondary figures (single GPU): the other configurations' shapes, graph-timed
+    extra = None
+    if world == 1 and os.environ.get("RB200_BENCH_NO_EXTRA", "0") != "1":
+        extra = {}
+
+        def graph_time(fn, calls=8, reps=3):
+            fn()
+            torch.cuda.synchronize()
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_):
+                for _ in range(calls):
+                    fn()
+            g_.replay()
+            torch.cuda.synchronize()
+            a_ = torch.cuda.Event(enable_timing=True)
+            b_ = torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(reps):
+                g_.replay()
+            b_.record()
+            torch.cuda.synchronize()
+            return a_.elapsed_time(b_) / (calls * reps)  # ms per call
+
+        gen2 = torch.Generator(device=dev)
+        gen2.manual_seed(3000)
+        # Llama-70B MLP, int8 per channel, 1/8 shards (gate_up column-parallel, down row-parallel)
+        for name, k3, n3 in (("gate_up_shard", 8192, 7168), ("down_shard", 3584, 8192)):
+            w8 = ops.preprocess_weight_ft(torch.randint(-127, 128, (k3, n3), dtype=torch.int8, device=dev,
+                                                        generator=gen2), False)
+            s8 = (torch.rand((n3,), device=dev, generator=gen2) * 0.0009 + 0.0001).half()
+            for m3 in (16, 256, 4096):
+                x3 = torch.randn((m3, k3), device=dev, generator=gen2).half()
+                o3 = torch.empty((m3, n3), device=dev, dtype=torch.float16)
+                torch.cuda.synchronize()
+                ms = graph_time(lambda: ops.gemm_fp16_ft(x3, w8, s8, 8, out=o3), calls=4 if m3 >= 4096 else 8)
+                extra["llama70b_int8_%s_m%d" % (name, m3)] = {
+                    "us": ms * 1e3, "tflops": 2.0 * m3 * k3 * n3 / (ms * 1e-3) / 1e12,
+                    "weight_gbs": k3 * n3 / (ms * 1e-3) / 1e9}
+            del w8, s8
+        # Mixtral expert layer: 512 tokens, top-2 of 8 experts, W4 group 128 (rows already sorted)
+        e4, k4, n4 = 8, 4096, 14336
+        logits = torch.randn((512, e4), device=dev, generator=gen2)
+        indptr4, tok4, gate4, rof4 = ops.moe_route(logits, 2)
+        w4 = ops.preprocess_weight_ft(torch.randint(-128, 128, (e4, k4, n4 // 2), dtype=torch.int8, device=dev,
+                                                    generator=gen2), True)
+        s4 = (torch.rand((e4, k4 // 128, n4), device=dev, generator=gen2) * 0.009 + 0.001).half()
+        x4 = torch.randn((1024, k4), device=dev, generator=gen2).half()
+        o4 = torch.empty((1024, n4), device=dev, dtype=torch.float16)
+        torch.cuda.synchronize()
+        ms = graph_time(lambda: ops.moe_gemm_ft(x4, w4, s4, indptr4, out=o4), calls=4)
+        extra["mixtral_moe_w4_g128_1024rows"] = {"us": ms * 1e3, "tflops": 2.0 * 1024 * k4 * n4 / (ms * 1e-3) / 1e12}
+        del w4, s4, x4, o4
+
     # ---- end-to-end timing through the PackedFunc surface with host buffers
     hx = {key: t.cpu().pin_memory() for key, t in xs.items()}
     hout = {key: torch.empty_like(t, device="cpu").pin_memory() for key, t in outs.items()}
@@ -472,6 +525,7 @@ def run_gpu(args):
             "clocks": {"sm_mhz": clk["sm_mhz"], "sm_max_mhz": clk["sm_max_mhz"], "reasons": clk["reasons"]},
             "max_rel_err_vs_oracle": max_rel_err,
             "prefill": prefill,
+            "extra": extra,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
