@@ -261,6 +261,8 @@ int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int
   RB200_CHECK(!(src_layout & RB200_LAYOUT_GATE_UP_INTERLEAVE) || n % 32 == 0,
               "the gate/up interleave needs n %% 32 == 0 (n=%lld)", (long long)n);
   RB200_CHECK(aligned16(dst), "dst must be 16-byte aligned");
+  RB200_CHECK(base_layout != RB200_LAYOUT_Q4_NK || (reinterpret_cast<uintptr_t>(src) & 7u) == 0,
+              "a q4f16_1 source must be 8-byte aligned");
   return preprocess_launch(src, dst, num_experts, k, n, bits, src_layout,
                            static_cast<cudaStream_t>(stream));
 }

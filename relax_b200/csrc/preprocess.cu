@@ -64,7 +64,29 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
     const int g = lane >> 2, t = lane & 3;
     const uint8_t* s = src + e * expert_bytes;
     uint32_t words[4];
-    if (BITS == 4) {
+    if (BITS == 4 && LAYOUT == 1) {
+      // q4f16_1 source: the unit's 16 k of a row are two consecutive 32-bit words of that row
+      // (8 nibbles each, k ascending from the low nibble): two 8-byte loads per unit, then bit moves
+      const int64_t k0 = kb * 64 + t * 16;
+      int64_t r_lo = nb * 16 + g, r_hi = r_lo + 8;
+      if (interleave) {
+        r_lo = gate_up_source_row(r_lo, N);
+        r_hi = gate_up_source_row(r_hi, N);
+      }
+      const uint2 lo = *reinterpret_cast<const uint2*>(s + (r_lo * (K / 8) + k0 / 8) * 4);
+      const uint2 hi = *reinterpret_cast<const uint2*>(s + (r_hi * (K / 8) + k0 / 8) * 4);
+      const uint32_t lw[2] = {lo.x, lo.y}, hw[2] = {hi.x, hi.y};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // word j covers k4 = 4j .. 4j+3: nibbles (j & 1) * 4 .. + 3 of source word j >> 1
+        const uint32_t a = (lw[j >> 1] >> ((j & 1) * 16)) & 0xffffu;  // row g:   k4+0..3 in nibbles 0..3
+        const uint32_t b = (hw[j >> 1] >> ((j & 1) * 16)) & 0xffffu;  // row g+8
+        // slots: p0 (g,k4) p4 (g,k4+1) p2 (g,k4+2) p6 (g,k4+3); p1 p5 p3 p7 the same for g+8
+        const uint32_t ga = (a & 0xfu) | ((a & 0xf0u) << 12) | ((a & 0xf00u)) | ((a & 0xf000u) << 12);
+        const uint32_t gb = (b & 0xfu) | ((b & 0xf0u) << 12) | ((b & 0xf00u)) | ((b & 0xf000u) << 12);
+        words[j] = ga | (gb << 4);
+      }
+    } else if (BITS == 4) {
       const int64_t k0 = kb * 64 + t * 16;
       // nibble slot p of a word <- (row offset, k offset inside the word's 4 k)
       const int row_of[8] = {0, 8, 0, 8, 0, 8, 0, 8};
