@@ -199,3 +199,30 @@ def test_layout_reference_roundtrip():
     codes8 = rs.randint(0, 256, size=(16, 64)).astype(np.uint8)
     lay8 = fragment_layout(codes8, 8)
     assert sorted(lay8.tolist()) == sorted(codes8.reshape(-1).tolist())
+
+
+def test_moe_route_restatement_invariants(oracle):
+    """np_moe_route: rows sorted by expert with ties broken by assignment order, indptr = end rows,
+    row_of_flat the inverse permutation, gates = the chosen softmax probabilities."""
+    g = np.random.Generator(np.random.PCG64(12))
+    t, e, k = 50, 8, 2
+    logits = g.standard_normal((t, e), dtype=np.float32)
+    logits[7] = 0.0  # all experts tie: the two lowest indices win
+    indptr, token_of_row, gate_of_row, row_of_flat = oracle.np_moe_route(logits, k)
+    assert indptr[-1] == t * k and np.all(np.diff(np.concatenate([[0], indptr])) >= 0)
+    p = np.exp(logits - logits.max(1, keepdims=True))
+    p /= p.sum(1, keepdims=True)
+    r0 = 0
+    for ex in range(e):
+        rows = np.arange(r0, indptr[ex])
+        # every row of the block belongs to a token that has `ex` among its top-k
+        for r in rows:
+            tok = token_of_row[r]
+            assert ex in np.argsort(-p[tok], kind="stable")[:k]
+            assert abs(gate_of_row[r] - p[tok, ex]) < 1e-7
+        assert np.all(np.diff(token_of_row[rows]) >= 0)  # stable: token order kept inside an expert
+        r0 = indptr[ex]
+    assert sorted(row_of_flat.tolist()) == list(range(t * k))
+    assert set(token_of_row[row_of_flat[7 * k:7 * k + k]].tolist()) == {7}
+    experts_of_7 = [int(np.searchsorted(indptr, r, side="right")) for r in row_of_flat[7 * k:7 * k + k]]
+    assert experts_of_7 == [0, 1]
