@@ -36,10 +36,25 @@ RB200_API int rb200_set_stream(void* stream);
 RB200_API void* rb200_get_stream(void);
 
 /*
- * Reads (and clears) the device-side status word that bounded waits inside the kernels set
- * when they give up.  Synchronises the given stream.  0 = no error recorded.
+ * Reads (and clears) the device-side status words that bounded waits inside the kernels set
+ * when they give up: the one in the library's per-device scratch block and the one in the static
+ * array of rb200_gemm_fp16_intx_noalloc.  Synchronises the given stream.  0 = no error recorded,
+ * 1 = a wait ran out (the kernel skipped its remaining work and left outputs unwritten).
+ * Allocates nothing: a status word that no call has created yet reads as 0.  After a non-zero
+ * status the split-k flags and tickets of the scratch block are put back at rest.
+ * Replaces nothing in the reference, whose kernels spin without a bound
+ * (3rdparty/tensorrt_llm/custom_allreduce_kernels.cu:94-113) and whose collectives abort the
+ * process on error (src/runtime/disco/nccl/nccl_context.h:50-56).
  */
 RB200_API int rb200_check_async_error(void* stream, int* status_out);
+
+/*
+ * Upper bound, in milliseconds, of every wait on a flag that another CTA or another GPU writes
+ * (split-k fix-up of the decode kernel, flag exchange of the all-reduce); 0 restores the default
+ * of about two seconds.  Process-wide; read when a kernel is launched.  A host that detects a
+ * missing peer by other means can set this short so that kernels already queued return quickly.
+ */
+RB200_API int rb200_set_wait_limit_ms(unsigned limit_ms);
 
 /*
  * Launch overlap for serving loops (process-wide switch, default off; no counterpart in the
@@ -175,13 +190,17 @@ RB200_API int rb200_gemm_fp16_int_bias_act_residual(
  * its split-k scratch is a fixed array inside the library image (about 5.06 MiB of device
  * memory on every GPU that loads the library, held until the process exits).
  *   Limits : m <= 16 and n <= 262144 (anything larger is rejected with an error, as is a
- *            problem whose partials would not fit); `workspace` in the descriptor is ignored.
+ *            problem whose partials would not fit); `workspace` in the descriptor is ignored;
+ *            RB200_ACT_SWIGLU and unknown activation / op codes are rejected (the kernel behind
+ *            this entry has no fused gate/up form).
  *   Set-up : the first call on each device resolves the array's device address and queries the
  *            device; make that first call with the device current and before any stream capture.
- *   Sharing: every call on a device uses the same array.  Each call clears the tickets and the
- *            status word it needs on `stream` before launching, so calls issued in stream order
- *            are independent; calls that overlap on the GPU (different streams, no dependency
- *            between them) race on the array and give undefined results.
+ *   Sharing: every call on a device uses the same array.  Each call clears the tickets it needs
+ *            on `stream` before launching, so calls issued in stream order are independent; calls
+ *            that overlap on the GPU (different streams, no dependency between them) race on the
+ *            array and give undefined results.
+ *   Status : a bounded wait that gives up sets the status word inside the array; it stays set
+ *            until rb200_check_async_error reads it, which allocates nothing either.
  */
 RB200_API int rb200_gemm_fp16_intx_noalloc(const rb200_gemm_desc* desc, void* stream);
 

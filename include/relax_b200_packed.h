@@ -44,6 +44,11 @@ typedef struct {
   int64_t* strides; /* NULL = compact row-major */
   uint64_t byte_offset;
 } DLTensor;
+typedef struct DLManagedTensor {
+  DLTensor dl_tensor;
+  void* manager_ctx;
+  void (*deleter)(struct DLManagedTensor* self);
+} DLManagedTensor;
 #endif
 
 /* ---- argument passing (c_runtime_api.h:174-215) ---- */
@@ -79,12 +84,16 @@ RB200_API int RB200FuncListGlobalNames(int* out_size, const char*** out_array);
 /*
  * Global functions registered by the library (all launch on rb200_get_stream()):
  *
- *  "cutlass.ft_preprocess_weight"(packed_weight, sm:int, is_int4:bool, out)
- *      src/runtime/contrib/cutlass/weight_preprocess.cc:38-58.  The reference returns a new
- *      NDArray; here `out` (same shape / dtype / device) is passed by the caller.  `sm` is
- *      accepted and must be 100 or the reference tests' 80 (ignored: one layout).  2-D
- *      [K, N(/2)] or 3-D [E, K, N(/2)] int8; CUDA tensors, or CPU tensors (staged through the
- *      device - there is no host implementation).
+ *  "cutlass.ft_preprocess_weight"(packed_weight, sm:int, is_int4:bool[, out])
+ *      src/runtime/contrib/cutlass/weight_preprocess.cc:38-58.  With the reference's own three
+ *      arguments the result is allocated on the input's device (cudaMalloc / malloc) and
+ *      returned as a DLManagedTensor* with type code RB200_ARG_HANDLE: the caller owns it and
+ *      releases it by calling its deleter (the reference returns its runtime's NDArray object,
+ *      which only that runtime can create; a bridge adopts the managed tensor with
+ *      NDArray::FromDLPack, no copy).  With a fourth argument `out` (same shape / dtype /
+ *      device) nothing is allocated and nothing is returned.  `sm` is accepted (70..120) and
+ *      ignored: one layout.  2-D [K, N(/2)] or 3-D [E, K, N(/2)] int8; CUDA tensors, or CPU
+ *      tensors (staged through the device - there is no host implementation).
  *  "relax_b200.preprocess_weight_q4f16"(packed_weight uint32 [N, K/8] or [E, N, K/8], out)
  *      the same step for the q4f16_1 layout of tests/python/dlight/test_gpu_gemv.py:189-206
  *      (no counterpart entry in the reference: it reaches that layout through generated TIR).

@@ -83,6 +83,7 @@ SIGNATURES = {
     "rb200_set_stream": (_I, [_V]),
     "rb200_get_stream": (_V, []),
     "rb200_check_async_error": (_I, [_V, ctypes.POINTER(_I)]),
+    "rb200_set_wait_limit_ms": (_I, [ctypes.c_uint]),
     "rb200_set_launch_overlap": (_I, [_I]),
     "rb200_get_launch_overlap": (_I, []),
     "rb200_preprocess_weight": (_I, [_V, _V, _I64, _I64, _I64, _I, _I, _V]),

@@ -41,6 +41,7 @@ struct ArParams {
   int rank_base;                 // real launch: this rank; self-test: 0 with gridDim.y = world
   long long count;               // fp16 elements
   long long region_bytes;        // size of one data region
+  unsigned long long wait_limit_ns;
   int* status;
 };
 
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArP
     while ((int32_t)(ld_acquire_sys(f) - call) < 0) {
       unsigned long long t1;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-      if (t1 - t0 > 2000000000ull) {  // two seconds: give up, report, leave the output unwritten
+      if (t1 - t0 > p.wait_limit_ns) {  // give up, report, leave the output unwritten
         if (p.status) atomicExch(p.status, kStatusWaitTimeout);
         s_fail = 1;
         break;
@@ -209,6 +210,7 @@ int rb200_allreduce_oneshot(void* const* workspaces, int rank, int world, const 
   p.count = count;
   p.region_bytes = region_bytes_for(max_count);
   p.status = sc->status;
+  p.wait_limit_ns = (wait_limit_ms() ? (unsigned long long)wait_limit_ms() : 2000ull) * 1000000ull;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)grid_for(count), 1, 1);
@@ -243,6 +245,7 @@ int rb200_allreduce_oneshot_selftest(void* const* workspaces, const void* const*
   p.count = count;
   p.region_bytes = region_bytes_for(max_count);
   p.status = sc->status;
+  p.wait_limit_ns = (wait_limit_ms() ? (unsigned long long)wait_limit_ms() : 2000ull) * 1000000ull;
   // all ranks' CTAs wait on one another: a cooperative launch guarantees they are co-resident
   void* args[] = {&p};
   RB200_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(allreduce_oneshot_kernel),

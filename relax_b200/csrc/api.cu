@@ -9,7 +9,6 @@
 #include "dequant.cuh"
 #include "gemv.h"
 #include "gemv_cluster.cuh"
-#include "umma_gemv.cuh"
 #include "umma_gemm.cuh"
 #include "gemv_sk.cuh"
 #include "gemm_tc.h"
@@ -33,9 +32,30 @@ void set_last_error(const char* fmt, ...) {
 // ---------------------------------------------------------------- per-device scratch
 namespace {
 constexpr int kMaxDevices = 64;
+// split-k flags of the stream-k decode kernel: inside the ticket area of the scratch block
+constexpr size_t kSkFlagOffset = 49152, kSkFlagCount = 16384;
 DeviceScratch g_scratch[kMaxDevices];
 std::mutex g_scratch_mutex;
 }  // namespace
+
+int sm_count_current() {
+  static std::atomic<int> cached[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+  cached[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+
+// The current device's scratch if it has been created, else nullptr: never allocates.
+DeviceScratch* device_scratch_if_any() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  return g_scratch[dev].base ? &g_scratch[dev] : nullptr;
+}
 
 DeviceScratch* device_scratch(size_t min_partial_bytes, size_t min_counter_ints) {
   int dev = 0;
@@ -203,7 +223,9 @@ using namespace rb200;
 
 namespace rb200 {
 static std::atomic<int> g_launch_overlap{0};
+static std::atomic<unsigned> g_wait_limit_ms{0};
 bool launch_overlap_enabled() { return g_launch_overlap.load(std::memory_order_relaxed) != 0; }
+unsigned wait_limit_ms() { return g_wait_limit_ms.load(std::memory_order_relaxed); }
 }  // namespace rb200
 
 extern "C" {
@@ -223,26 +245,32 @@ int rb200_set_stream(void* stream) {
 void* rb200_get_stream(void) { return g_stream; }
 
 int rb200_check_async_error(void* stream, int* status_out) {
-  DeviceScratch* sc = device_scratch(0, 0);
-  if (!sc) return -1;
+  // Two status words can exist on a device: the one in the library's lazily allocated scratch
+  // block (every entry point but the no-alloc one) and the one in the no-alloc entry's static
+  // array.  Neither is created here: a host that only ever used the no-alloc entry must be
+  // able to ask without triggering a device allocation.
   int st = 0;
   RB200_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-  RB200_CUDA(cudaMemcpy(&st, sc->status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (st != 0) RB200_CUDA(cudaMemset(sc->status, 0, sizeof(int)));
+  if (DeviceScratch* sc = device_scratch_if_any()) {
+    int v = 0;
+    RB200_CUDA(cudaMemcpy(&v, sc->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) {
+      // a wait that gave up may have left split-k flags and tickets behind: back to rest
+      RB200_CUDA(cudaMemset(sc->base, 0, (size_t)(reinterpret_cast<uint8_t*>(sc->partials) - static_cast<uint8_t*>(sc->base))));
+      st = v;
+    }
+  }
+  int v2 = 0;
+  if (noalloc_read_status(&v2) != 0) return -1;
+  if (st == 0) st = v2;
   if (status_out) *status_out = st;
   return 0;
 }
 
-#ifdef RB200_ABLATE
-// instrumented builds only: copy a range of the library's partial-sum scratch to the host
-RB200_API int rb200_debug_read_scratch(void* dst, size_t offset_bytes, size_t bytes) {
-  DeviceScratch* sc = device_scratch(0, 0);
-  if (!sc) return -1;
-  RB200_CUDA(cudaDeviceSynchronize());
-  RB200_CUDA(cudaMemcpy(dst, reinterpret_cast<uint8_t*>(sc->partials) + offset_bytes, bytes, cudaMemcpyDeviceToHost));
+int rb200_set_wait_limit_ms(unsigned limit_ms) {
+  g_wait_limit_ms.store(limit_ms, std::memory_order_relaxed);
   return 0;
 }
-#endif
 
 int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int64_t k, int64_t n,
                             int is_int4, int src_layout, void* stream) {
@@ -307,6 +335,12 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     RB200_CHECK(d->n % 32 == 0, "the fused gate/up activation needs n %% 32 == 0");
   }
   RB200_CHECK(d->bias_stride == 0 || d->bias_stride == d->n, "bias_stride must be 0 or n");
+  RB200_CHECK(d->activation >= RB200_ACT_IDENTITY && d->activation <= RB200_ACT_SWIGLU, "unknown activation code %d",
+              d->activation);
+  RB200_CHECK(d->binary_op >= RB200_BIN_NONE && d->binary_op <= RB200_BIN_MULTIPLY, "unknown binary_op code %d",
+              d->binary_op);
+  RB200_CHECK(d->unary_op >= RB200_UN_IDENTITY && d->unary_op <= RB200_UN_RELU, "unknown unary_op code %d",
+              d->unary_op);
 
   Epilogue epi;
   epi.bias = static_cast<const __half*>(d->bias);
@@ -318,9 +352,7 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
   epi.unop = d->unary_op;
   const int group = (d->group_size <= 0 || d->group_size >= d->k) ? 0 : (int)d->group_size;
 
-  static const bool force_scratch_path = getenv("RB200_GEMV_SCRATCH_PATH") != nullptr;
-  if (d->m <= 32 && !d->workspace && (!force_scratch_path || swiglu)) {
-    // default decode path: cluster split-k, no global scratch beyond the status word
+  if (d->m <= 32 && !d->workspace) {
     DeviceScratch* sc = device_scratch(0, 0);
     if (!sc) return -1;
     GemvParams p;
@@ -341,51 +373,22 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
-#ifdef RB200_ABLATE
-    {
-      const char* ab = getenv("RB200_GEMV_ABLATE");
-      p.ablate = ab ? atoi(ab) : 0;
-    }
-#endif
-    {
-      // epoch flags live past the ticket area of the scratch block
-      constexpr size_t kFlagOffset = 49152, kFlagCount = 16384;
-      unsigned* flags = reinterpret_cast<unsigned*>(sc->counters) + kFlagOffset;
-      const unsigned epoch = ++sc->epoch;
-      // Which decode kernel: measured crossovers on B200.  Few 128-row tiles (n <= 4096): the
-      // cluster kernel, whose split-k partials meet in distributed shared memory, beats the
-      // global slot + flag fix-up by about 3 us.  Otherwise the stream-k warp-MMA kernel.  The
-      // tcgen05 decode kernel (RB200_GEMV_KERNEL=1) loses to both at every measured shape - one
-      // tcgen05.mma costs ~172 clocks whatever the batch - and is kept for comparison only.
-      static const int forced = getenv("RB200_GEMV_KERNEL") ? atoi(getenv("RB200_GEMV_KERNEL")) : -1;
-      int which = 0;
-      if (p.n <= 4096) which = 2;
-      if (forced >= 0) which = forced;
-      if (swiglu && which == 1) which = 0;  // the comparison kernel has no fused gate/up epilogue
-      if (which == 0)
-        return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
-                           kFlagCount, epoch, stream);
-      if (which == 1) {
-        const int rc = umma_gemv_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials,
-                                     sc->partial_bytes, flags, kFlagCount, epoch, stream);
-        if (rc < 0) return rc;
-        if (rc == 0) return 0;
-        return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
-                           kFlagCount, epoch, stream);
-      }
+    // Which decode kernel: measured crossover on B200.  Few 128-row tiles (n <= 4096): the
+    // cluster kernel, whose split-k partials meet in distributed shared memory.  Otherwise the
+    // stream-k kernel (split-k flags live past the ticket area of the scratch block).
+    if (p.n > 4096) {
+      unsigned* flags = reinterpret_cast<unsigned*>(sc->counters) + kSkFlagOffset;
+      return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
+                         kSkFlagCount, stream);
     }
     return gemv_cluster_run(p, d->weight_bits, zero_mode(d), sc->sm_count, stream);
   }
   if (d->m <= 32) {
-    // caller-provided workspace (or RB200_GEMV_SCRATCH_PATH): stream-k kernel with global partials
+    // caller-provided workspace: the ticket-based split-k kernel, partials in the caller's memory
     DeviceScratch* sc = device_scratch(0, 0);
     if (!sc) return -1;
     GemvPlan plan;
-    const char* env_c = getenv("RB200_GEMV_CTAS_PER_SM");
-    const char* env_s = getenv("RB200_GEMV_STAGES");
-    if (gemv_plan(d->weight_bits, (int)d->m, (int)d->n, (int)d->k, sc->sm_count,
-                  env_c ? atoi(env_c) : 0, env_s ? atoi(env_s) : 0, &plan) != 0)
-      return -1;
+    if (gemv_plan(d->weight_bits, (int)d->m, (int)d->n, (int)d->k, sc->sm_count, 0, 0, &plan) != 0) return -1;
     GemvParams p;
     memset(&p, 0, sizeof(p));
     if (d->workspace) {
@@ -419,15 +422,9 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
-#ifdef RB200_ABLATE
-    {
-      const char* ab = getenv("RB200_GEMV_ABLATE");
-      p.ablate = ab ? atoi(ab) : 0;
-    }
-#endif
     return gemv_launch(p, plan, d->weight_bits, zero_mode(d), stream);
   }
-  return gemm_tc_launch(d, epi, group, zero_mode(d), stream);
+  return gemm_tc_launch(d, epi, group, zero_mode(d), ldx, ldo, stream);
 }
 
 static int fill_ft_desc(rb200_gemm_desc* d, const void* A, const void* B, const void* scales,
@@ -539,7 +536,8 @@ int rb200_dequantize(const rb200_gemm_desc* d, void* wq_out, void* stream_v) {
   const int frag = d->weight_bits == 4 ? 64 : 32;
   int64_t tiles = (d->n / 16) * (d->k / frag);
   int64_t blocks = (tiles + 7) / 8;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const int64_t max_blocks = (int64_t)sm_count_current() * 16;
+  if (blocks > max_blocks) blocks = max_blocks;
   const uint8_t* w = static_cast<const uint8_t*>(d->w);
   const __half* s = static_cast<const __half*>(d->scales);
   const __half* z = static_cast<const __half*>(d->zeros);

@@ -43,16 +43,26 @@ struct DeviceScratch {
   float* partials = nullptr;
   size_t partial_bytes = 0;
   int sm_count = 0;
-  unsigned epoch = 0;       // launch counter for epoch-valued flags (tcgen05 decode kernel)
 };
 // Returns the current device's scratch, allocating it on first use (never inside a capture:
 // call once during warm-up).  nullptr + last error set on failure.
 DeviceScratch* device_scratch(size_t min_partial_bytes, size_t min_counter_ints);
+// The current device's scratch if some earlier call created it, else nullptr; never allocates.
+DeviceScratch* device_scratch_if_any();
+// Status word of the no-alloc entry point's static array on the current device (0 when that
+// entry has not been used on it); reads and clears it without allocating anything.
+int noalloc_read_status(int* status_out);
+// Upper bound, in milliseconds, of the waits on flags written by other CTAs or other GPUs
+// (split-k fix-up, all-reduce); 0 = the default of about two seconds.  See rb200_set_wait_limit_ms.
+unsigned wait_limit_ms();
 
 // Launch overlap (programmatic dependent launch): when the host enabled it, matmul kernels are
 // launched so that they may start - and stream their weights - while the previous kernel on the
 // stream is still finishing.  See rb200_set_launch_overlap in the public header.
 bool launch_overlap_enabled();
+
+// Number of SMs of the current device (queried once per device, no allocation).
+int sm_count_current();
 
 // Status codes written to the device status word.
 enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadConfig = 2 };

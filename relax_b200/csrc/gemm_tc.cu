@@ -10,9 +10,8 @@
 
 namespace rb200 {
 
-int gemm_tc_launch(const rb200_gemm_desc* d, const Epilogue& epi, int group, int zmode, cudaStream_t stream) {
-  const int64_t ldx = d->ldx > 0 ? d->ldx : d->k;
-  const int64_t ldo = d->ldo > 0 ? d->ldo : d->n;
+int gemm_tc_launch(const rb200_gemm_desc* d, const Epilogue& epi, int group, int zmode, int64_t ldx, int64_t ldo,
+                   cudaStream_t stream) {
   DeviceScratch* sc = device_scratch(0, 0);
   if (!sc) return -1;
   {
@@ -34,13 +33,6 @@ int gemm_tc_launch(const rb200_gemm_desc* d, const Epilogue& epi, int group, int
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
-#ifdef RB200_ABLATE
-    {
-      const char* ab = getenv("RB200_GEMV_ABLATE");
-      p.ablate = ab ? atoi(ab) : 0;
-      p.partial = sc->partials;
-    }
-#endif
     const int rc = umma_gemm_run(p, d->weight_bits, zmode, sc->sm_count, stream);
     if (rc <= 0) return rc;
   }
@@ -52,7 +44,7 @@ int gemm_tc_launch(const rb200_gemm_desc* d, const Epilogue& epi, int group, int
     s.ldx = ldx;
     s.ldo = ldo;
     if (d->bias && d->bias_stride != 0) s.bias = static_cast<const char*>(d->bias) + m0 * d->bias_stride * 2;
-    if (d->residual) s.residual = static_cast<const char*>(d->residual) + m0 * d->n * 2;
+    if (d->residual) s.residual = static_cast<const char*>(d->residual) + m0 * d->n * 2;  // residual rows are n wide
     if (rb200_gemm_fp16_intx(&s, stream) != 0) return -1;
   }
   return 0;

@@ -84,12 +84,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
   fence_proxy_async();
   __syncthreads();
 
-#ifdef RB200_ABLATE
-  const int ablate = p.ablate;
-  if (ablate & 8) return;
-#else
-  constexpr int ablate = 0;
-#endif
   const long long total = p.total_iters;
   const long long grid = gridDim.x;
   const long long it0 = range_start(blockIdx.x, total, grid);
@@ -157,10 +151,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
                           uint32_t (&zv)[SP::kCount]) {
     const int blk = (int)tile_i * kConsumerWarps + warp;
     if (blk >= n_blocks) return;
-    if (ablate & 2) {
-      for (int i = 0; i < SP::kCount; ++i) sv[i] = 0x3c003c00u, zv[i] = 0;
-      return;
-    }
     const int64_t n_g = (int64_t)blk * 16 + g;
 #pragma unroll
     for (int i = 0; i < SP::kCount; ++i) {
@@ -208,7 +198,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
     const int nkb = min(kBlocksPerChunk, kb_total - kb0);
     const int blk = (int)tile * kConsumerWarps + warp;
     const uint8_t* sbase = smem + (size_t)stage * kStage;
-    if (blk < n_blocks && !(ablate & 4)) {
+    if (blk < n_blocks) {
       const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * (nkb * kTileBytes));
       const uint8_t* xsm = sbase + G::kWBytes + g * G::kXPitch + t * (G::kFrag / 2);
 #pragma unroll
@@ -271,7 +261,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p) {
       if (blk < n_blocks) {
         const bool whole = (seg_first_chunk == 0) && tile_end;
         bool do_store = whole;
-        if (!whole && !(ablate & 1)) {
+        if (!whole) {
           const int slot = (int)blockIdx.x * 2 + (first_segment ? 0 : 1);
           float* dst = p.partial + ((size_t)(slot * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll

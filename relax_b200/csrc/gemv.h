@@ -25,9 +25,6 @@ struct GemvParams {
   int stages;
   int chunks_per_tile;
   long long total_iters;
-#ifdef RB200_ABLATE
-  int ablate;
-#endif
 };
 
 struct GemvPlan {

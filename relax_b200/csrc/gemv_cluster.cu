@@ -49,8 +49,7 @@ int gemv_cluster_run(const GemvParams& p_in, int bits, int zmode, int sm_count, 
   const int64_t kg = l.group_code > 0 ? p.k / p.group : 0;
   const bool z_ok = p.z == nullptr || (reinterpret_cast<uintptr_t>(p.z) & 15u) == 0;
   const bool s_al = (reinterpret_cast<uintptr_t>(p.s) & 15u) == 0 && z_ok;
-  static const bool no_tma = getenv("RB200_GEMV_NO_SCALE_TMA") != nullptr;
-  if (l.group_code > 0 && s_al && !no_tma) {
+  if (l.group_code > 0 && s_al) {
     if (p.s_g == 1 && p.s_n == kg && bits == 4 && p.group == 32 && (kg * 2) % 16 == 0)
       l.src = kSrcSmemNK;
     else if (p.s_n == 1 && p.s_g == p.n && chunk % p.group == 0)
@@ -92,15 +91,10 @@ int gemv_cluster_run(const GemvParams& p_in, int bits, int zmode, int sm_count, 
   p.chunks_per_tile = cpt;
   p.total_iters = (long long)cpt * n_tiles;
 
-  static const int env_split = getenv("RB200_GEMV_SPLIT") ? atoi(getenv("RB200_GEMV_SPLIT")) : 0;
-  static const int env_stages = getenv("RB200_GEMV_STAGES") ? atoi(getenv("RB200_GEMV_STAGES")) : 0;
-  static const int env_ctas = getenv("RB200_GEMV_CTAS_PER_SM") ? atoi(getenv("RB200_GEMV_CTAS_PER_SM")) : 0;
   l.n_tiles = n_tiles;
   l.cpt = cpt;
   l.sm_count = sm_count;
-  l.ctas_per_sm = env_ctas > 0 ? env_ctas : 2;
-  l.force_split = env_split;
-  l.force_stages = env_stages;
+  l.ctas_per_sm = 2;
   l.stage_bytes = cluster_stage_bytes(bits, l.mt, zmode, l.src);
   l.fixed_bytes = (size_t)2 * kConsumerWarps * l.mt * 512;
 

@@ -492,8 +492,6 @@ struct ClusterLaunch {
   int bits, mt, zmode, group_code, src;
   int n_tiles, cpt, sm_count;
   int ctas_per_sm;      // residency target used to size the pipeline
-  int force_split;      // > 0: use this split factor (diagnostics)
-  int force_stages;     // > 0: use this many pipeline stages (diagnostics)
   size_t stage_bytes;   // one pipeline stage
   size_t fixed_bytes;   // partial-fragment buffers
 };

@@ -28,7 +28,6 @@ int launch_inst(ClusterParams cp, const ClusterLaunch& l, const CUtensorMap& ts,
   // pipeline depth from the per-CTA shared-memory budget (1 KB per CTA is reserved by the system)
   const size_t budget = (size_t)(228 * 1024) / l.ctas_per_sm - 1024;
   int stages = (int)((budget - l.fixed_bytes - 64) / l.stage_bytes);
-  if (l.force_stages > 0) stages = l.force_stages;
   if (stages > 12) stages = 12;
   if (stages < 1) stages = 1;
   const size_t smem = smem_for(l, stages);
@@ -72,7 +71,6 @@ int launch_inst(ClusterParams cp, const ClusterLaunch& l, const CUtensorMap& ts,
   for (int i = 0; i < 4; ++i) {
     const int s = 1 << i;
     if (s > l.cpt || max_clusters[i] <= 0) continue;
-    if (l.force_split > 0 && s != l.force_split) continue;
     const int nc = l.n_tiles < max_clusters[i] ? l.n_tiles : max_clusters[i];
     const int rounds = (l.n_tiles + nc - 1) / nc;
     const double cost = rounds * ((double)((l.cpt + s - 1) / s) + (s > 1 ? 0.6 : 0.0));

@@ -7,7 +7,7 @@
 namespace rb200 {
 
 int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float* partial, size_t partial_bytes,
-                unsigned* flags, size_t flag_count, unsigned epoch, cudaStream_t stream) {
+                unsigned* flags, size_t flag_count, cudaStream_t stream) {
   using namespace sk;
   const int frag = bits == 4 ? 64 : 32;
   const int chunk = frag * kBlocksPerChunk;
@@ -37,8 +37,7 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   const int64_t kg = l.group_code != 0 ? p.k / p.group : 0;
   const bool al = (reinterpret_cast<uintptr_t>(p.s) & 15u) == 0 &&
                   (p.z == nullptr || (reinterpret_cast<uintptr_t>(p.z) & 15u) == 0);
-  static const bool no_stage = getenv("RB200_GEMV_NO_SCALE_STAGING") != nullptr;
-  if (l.group_code > 0 && al && !no_stage) {
+  if (l.group_code > 0 && al) {
     if (p.s_g == 1 && p.s_n == kg && bits == 4 && p.group == 32 && (kg * 2) % 16 == 0) l.src = kSrcSmemNK;
     else if (p.s_n == 1 && p.s_g == p.n && chunk % p.group == 0 && p.n % 8 == 0) l.src = kSrcSmemKN;
   }
@@ -49,15 +48,12 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   p.chunks_per_tile = cpt;
   p.total_iters = (long long)cpt * n_tiles;
 
-  static const int env_stages = getenv("RB200_GEMV_STAGES") ? atoi(getenv("RB200_GEMV_STAGES")) : 0;
-  static const int env_ctas = getenv("RB200_GEMV_CTAS_PER_SM") ? atoi(getenv("RB200_GEMV_CTAS_PER_SM")) : 0;
-  const int ctas_per_sm = env_ctas > 0 ? env_ctas : 2;
+  const int ctas_per_sm = 2;
   const int xpitch = chunk * 2 + (bits == 4 ? 16 : 64);
   size_t sb = (size_t)kConsumerWarps * kBlocksPerChunk * kTileBytes + (size_t)((l.mt * 8 * xpitch + 127) / 128) * 128;
   if (l.src != kSrcGlobal) sb += kScaleBoxBytes * (zmode == kZeroGeneral ? 2 : 1);
   const size_t budget = (size_t)(228 * 1024) / ctas_per_sm - 1024;
   int stages = (int)((budget - 512) / sb);
-  if (env_stages > 0) stages = env_stages;
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
   p.stages = stages;
@@ -71,7 +67,7 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
               "split-k scratch too small: need %zu bytes and %d flags", need, l.grid * kConsumerWarps);
   pp.partial = partial;
   pp.flags = flags;
-  pp.epoch = epoch;
+  pp.wait_limit_ms = wait_limit_ms();
   if (bits == 4) return launch_sk_i4(pp, l, stream);
   return launch_sk_i8(pp, l, stream);
 }

@@ -3,27 +3,37 @@
 // What measurements on B200 settled before this version was written:
 //  * mma.sync.m16n8k16 sustains one MMA per 8 clocks per SM sub-partition - a 16x16 weight
 //    fragment (128 packed bytes) per 2 clocks per SM, far above the HBM rate - while tcgen05.mma
-//    costs about 172 clocks per instruction whatever N is, so with the batch as N (<= 32) the
-//    5th-generation tensor cores cap the weight stream near 2.6 TB/s.  Small batches belong on
-//    the warp MMA; tcgen05 pays off from a batch of a hundred rows up.
+//    pays off only from a batch of a hundred rows up.  Small batches belong on the warp MMA.
 //  * the async copy engine is paid per contiguous segment (about 170 clocks each when one thread
-//    issues them), not per byte: a stage made of 8 weight slices plus one copy per x row halves
-//    an SM's streaming rate.  Hence the stage-contiguous fragment layout (one 16 KB bulk copy
-//    per stage) and a loader warp that moves x and the scale tiles with 16-byte cp.async.
+//    issues them), not per byte.  Hence the stage-contiguous fragment layout (one 16 KB bulk copy
+//    per stage) and 16-byte cp.async for x and the scale tiles.
+//  * the kernel is bound by instruction issue, not by bytes: every warp that polls a barrier
+//    takes issue slots from the eight warps doing the arithmetic.  So one feeder warp (not two)
+//    serves the ring, it sleeps between polls, and the consumers' inner loop carries no test
+//    that can be decided outside it (ragged last chunk, inactive row block).
 //  * global fix-up through fences and tickets costs 6-8 us per launch.  Here a CTA does the
-//    pieces of tiles it shares with neighbours first (the tail piece goes to a global slot + an
-//    epoch flag right away, the head piece stays in registers), then its whole tiles, and only
-//    at the very end adds the neighbours' slots - written long before - to its head piece.
+//    pieces of tiles it shares with neighbours first (the tail piece goes to a global slot + a
+//    flag right away, the head piece stays in registers), then its whole tiles, and only at the
+//    very end adds the neighbours' slots - written long before - to its head piece.
 //
-//   producer warp : one bulk async copy per (128-row tile, k-chunk) stage
-//   loader warp   : x slice + scale / zero tiles by cp.async, counted on the stage's mbarrier
+//   feeder warp   : per (128-row tile, k-chunk) stage one bulk async copy of the packed weights
+//                   (lane 0), the scale / zero tiles and the x slice by 16-byte cp.async (all
+//                   lanes), everything counted on the stage's mbarrier.  Weights and scales of
+//                   the first ring-full of stages are requested before the kernel waits for its
+//                   predecessor on the stream; x only after.
 //   8 consumers   : one 16-row block each; 128-bit fragment words from shared memory, bit-exact
-//                   decode in registers, m16n8k16 MMAs into fp32 fragments (two chains)
+//                   decode in registers, m16n8k16 MMAs into fp32 fragments
+//
+// Split-k flags are plain 0 / 1 words: the writer of a tail piece sets its flag after the
+// partial sums, the one owner that consumes the piece clears it again, so a launch leaves the
+// flags as it found them and a CUDA graph may replay it any number of times.
 //
 // Stands in for fastertransformer::gemm_fp16_int_bias_act[_residual] at small m
 // (python/tvm/contrib/cutlass/gemm_operation.py:441-458) and the reference's GEMV / LowBatchGEMV
 // schedules (python/tvm/dlight/gpu/gemv.py:216-530, low_batch_gemv.py:300-613).
 #pragma once
+
+#include <type_traits>
 
 #include "dequant.cuh"
 #include "gemv.h"
@@ -32,7 +42,7 @@ namespace rb200 {
 namespace sk {
 
 constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 2) * 32;  // + producer + loader
+constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + feeder
 constexpr int kTileRows = kConsumerWarps * 16;
 constexpr int kBlocksPerChunk = 4;
 constexpr int kTileBytes = 512;
@@ -61,9 +71,9 @@ struct StageLayout {
 struct Params {
   GemvParams g;
   float* partial;     // [grid][2][8 warps][MT][4][32] fp32: slot 0 tail piece (for the owner), slot 1 own head piece
-  unsigned* flags;    // [grid][8] epoch flags, one per consumer warp
-  unsigned epoch;
+  unsigned* flags;    // [grid][8]: 1 while a tail piece waits for its owner, 0 at rest
   int has_z_tile;
+  unsigned wait_limit_ms;  // bound of the fix-up wait (0: about two seconds)
 };
 
 #ifdef __CUDACC__
@@ -144,11 +154,20 @@ struct ScalePlan {
   static constexpr int kCount = kChunk / kSpan;
 };
 
+// Feeder-side wait: a failed poll is followed by a sleep, so a feeder that is ahead of the
+// consumers costs them next to no issue slots.  Bounded like every other wait.
+__device__ __forceinline__ bool mbar_wait_sleepy(uint64_t* bar, uint32_t parity, int* status) {
+#pragma unroll 1
+  for (int i = 0; i < (1 << 23); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(200);
+  }
+  if (status) atomicExch(status, kStatusWaitTimeout);
+  return false;
+}
+
 template <int BITS, int MT, int ZMODE, int GROUP, int SRC>
-#ifndef RB200_SK_CTAS_MT1
-#define RB200_SK_CTAS_MT1 2
-#endif
-__global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gemv_sk_kernel(const Params pp) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   using G = Geo<BITS>;
   using L = StageLayout<BITS, MT, ZMODE, SRC>;
   using SP = ScalePlan<BITS, GROUP>;
@@ -164,18 +183,14 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStage);
   uint64_t* empty_bar = full_bar + stages;
 
-  // x rows >= m are never written by the loader and must read as zero
+  // x rows >= m are never written by the feeder and must read as zero
   for (int s = 0; s < stages; ++s) {
     uint32_t* xs = reinterpret_cast<uint32_t*>(smem + (size_t)s * kStage + G::kWBytes);
     for (int i = tid; i < L::kXBytes / 4; i += kThreads) xs[i] = 0u;
   }
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
-#ifdef RB200_SK_LAG
-      mbar_init(&full_bar[s], 2);
-#else
-      mbar_init(&full_bar[s], 1 + 32);  // producer's expect_tx arrival + 32 loader lanes
-#endif
+      mbar_init(&full_bar[s], 1 + 32);  // lane 0's expect_tx arrival + 32 lanes of cp.async
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
     mbar_fence_init();
@@ -184,130 +199,116 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
   __syncthreads();
   griddep_launch_dependents();
 
-#ifdef RB200_ABLATE
-  const int ablate = p.ablate;
-#else
-  constexpr int ablate = 0;
-#endif
+  const int cta = blockIdx.x;
   const long long total = p.total_iters;
   const long long grid = gridDim.x;
-  const long long it0 = range_start(blockIdx.x, total, grid);
-  const long long it1 = range_start(blockIdx.x + 1, total, grid);
+  const long long it0 = range_start(cta, total, grid);
+  const long long it1 = range_start(cta + 1, total, grid);
   const int cpt = p.chunks_per_tile;
   const int kb_total = p.k / G::kFrag;
   const int n_blocks = p.n / 16;
 
   if (warp == kConsumerWarps) {
-    // ------------------------------------------------------------ producer: packed weights
-    int stage = 0;
-    uint32_t phase = 0;
-    Piece pc;
-    bool ok = true;
-    for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, pc); ++idx) {
-      const int nblk = min(kConsumerWarps, n_blocks - pc.tile * kConsumerWarps);
-      for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
-        if (!mbar_wait_parked(&empty_bar[stage], phase ^ 1u, p.status)) {
-          ok = false;
-          break;
-        }
-        if (lane == 0) {
-          const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
-          const uint32_t wbytes = (uint32_t)(nkb * nblk) * kTileBytes;  // contiguous in the fragment layout
-          mbar_arrive_expect_tx(&full_bar[stage], wbytes);
-          bulk_g2s(smem + (size_t)stage * kStage, p.w + frag_stage_offset(pc.tile, chunk, n_blocks, kb_total),
-                   wbytes, &full_bar[stage]);
-        }
-        __syncwarp();
-        if (++stage == stages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-    }
-    return;
-  }
-  if (warp == kConsumerWarps + 1) {
-    // ------------------------------------------------------------ loader: x, scales, zeros
-    int stage = 0;
-    uint32_t phase = 0;
-    Piece pc;
-    bool ok = true;
+    // ------------------------------------------------------------ feeder
     const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
     constexpr int kXChunks = G::kChunk * 2 / 16;  // 16-byte pieces per x row per stage (32 / 16)
-    bool dep_waited = false;
-#ifdef RB200_SK_LAG
-    int lag_issued = 0, lag_stage = 0;
-#endif
-    for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, pc); ++idx) {
-      const int64_t n0 = (int64_t)pc.tile * kTileRows;
-      for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
-        if (!mbar_wait_parked(&empty_bar[stage], phase ^ 1u, p.status)) {
-          ok = false;
-          break;
-        }
-        uint8_t* sbase = smem + (size_t)stage * kStage;
-        if (SRC == kSrcSmemNK) {
-          // [128 rows][8 groups]: 16 bytes per row
-          const int64_t g0 = (int64_t)chunk * 8;
-          const int64_t left = (kg - g0) * 2;
-          const uint32_t sv = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+
+    auto feed_w = [&](int tile, int chunk, int stage) {  // packed weights + scale / zero tiles
+      uint8_t* sbase = smem + (size_t)stage * kStage;
+      if (lane == 0) {
+        const int nblk = min(kConsumerWarps, n_blocks - tile * kConsumerWarps);
+        const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
+        const uint32_t wbytes = (uint32_t)(nkb * nblk) * kTileBytes;  // contiguous in the fragment layout
+        mbar_arrive_expect_tx(&full_bar[stage], wbytes);
+        bulk_g2s(sbase, p.w + frag_stage_offset(tile, chunk, n_blocks, kb_total), wbytes, &full_bar[stage]);
+      }
+      const int64_t n0 = (int64_t)tile * kTileRows;
+      if (SRC == kSrcSmemNK) {
+        // [128 rows][8 groups]: 16 bytes per row
+        const int64_t g0 = (int64_t)chunk * 8;
+        const int64_t left = (kg - g0) * 2;
+        const uint32_t sv = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int row = lane + 32 * i;
-            const bool in = n0 + row < p.n;
-            const int64_t o = (in ? (n0 + row) : 0) * kg + (sv ? g0 : 0);
-            cp_async16(sbase + L::kSOff + row * 16, p.s + o, in ? sv : 0u);
-            if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + L::kZOff + row * 16, p.z + o, in ? sv : 0u);
-          }
-        } else if (SRC == kSrcSmemKN) {
-          // [groups of the chunk][128 rows]: 256 bytes per group row
-          constexpr int kG = GROUP > 0 ? (G::kChunk / GROUP) : 1;
-          for (int i = lane; i < kG * 16; i += 32) {
-            const int gl = i >> 4, cc = i & 15;
-            const int64_t grow = (int64_t)chunk * kG + gl;
-            const bool in = grow < kg && n0 + cc * 8 < p.n;
-            const int64_t o = (in ? grow : 0) * p.n + (in ? n0 + cc * 8 : 0);
-            cp_async16(sbase + L::kSOff + gl * 256 + cc * 16, p.s + o, in ? 16u : 0u);
-            if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + L::kZOff + gl * 256 + cc * 16, p.z + o, in ? 16u : 0u);
-          }
+        for (int i = 0; i < 4; ++i) {
+          const int row = lane + 32 * i;
+          const bool in = n0 + row < p.n;
+          const int64_t o = (in ? (n0 + row) : 0) * kg + (sv ? g0 : 0);
+          cp_async16(sbase + L::kSOff + row * 16, p.s + o, in ? sv : 0u);
+          if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + L::kZOff + row * 16, p.z + o, in ? sv : 0u);
         }
-        // activations may come from the previous kernel on the stream: read them after it ended
-        if (!dep_waited) {
-          griddep_wait();
-          dep_waited = true;
+      } else if (SRC == kSrcSmemKN) {
+        // [groups of the chunk][128 rows]: 256 bytes per group row
+        constexpr int kG = GROUP > 0 ? (G::kChunk / GROUP) : 1;
+        for (int i = lane; i < kG * 16; i += 32) {
+          const int gl = i >> 4, cc = i & 15;
+          const int64_t grow = (int64_t)chunk * kG + gl;
+          const bool in = grow < kg && n0 + cc * 8 < p.n;
+          const int64_t o = (in ? grow : 0) * p.n + (in ? n0 + cc * 8 : 0);
+          cp_async16(sbase + L::kSOff + gl * 256 + cc * 16, p.s + o, in ? 16u : 0u);
+          if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + L::kZOff + gl * 256 + cc * 16, p.z + o, in ? 16u : 0u);
         }
-        // x[r, chunk*kChunk + c*8 .. +8) -> row r of the stage's x tile
-        for (int i = lane; i < p.m * kXChunks; i += 32) {
-          const int r = i / kXChunks, c = i % kXChunks;
-          const int64_t kcol = (int64_t)chunk * G::kChunk + c * 8;
-          const uint32_t v = kcol < p.k ? 16u : 0u;
-          cp_async16(sbase + G::kWBytes + r * G::kXPitch + c * 16, p.x + (int64_t)r * p.ldx + (v ? kcol : 0), v);
-        }
-#ifdef RB200_SK_LAG
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (++lag_issued > 2) {
-          asm volatile("cp.async.wait_group 2;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[lag_stage]);
-          if (++lag_stage == stages) lag_stage = 0;
-        }
-#else
-        cp_async_arrive(&full_bar[stage]);
-#endif
-        if (++stage == stages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+      }
+    };
+    auto feed_x = [&](int chunk, int stage) {  // x[r, chunk*kChunk + c*8 .. +8) -> row r of the stage's x tile
+      uint8_t* sbase = smem + (size_t)stage * kStage;
+      for (int i = lane; i < p.m * kXChunks; i += 32) {
+        const int r = i / kXChunks, c = i % kXChunks;
+        const int64_t kcol = (int64_t)chunk * G::kChunk + c * 8;
+        const uint32_t v = kcol < p.k ? 16u : 0u;
+        cp_async16(sbase + G::kWBytes + r * G::kXPitch + c * 16, p.x + (int64_t)r * p.ldx + (v ? kcol : 0), v);
+      }
+      cp_async_arrive(&full_bar[stage]);
+    };
+
+    // The first ring-full of stages needs no wait (every stage starts empty): request their
+    // weights and scales at once, then wait for the previous kernel on the stream - activations
+    // may be its output - and only then fetch x for them.
+    Piece pc;
+    int idx = 0, chunk = 0;
+    bool have = get_piece(it0, it1, cpt, 0, pc);
+    if (have) chunk = pc.c0;
+    auto advance = [&]() {
+      if (++chunk >= pc.c1) {
+        have = get_piece(it0, it1, cpt, ++idx, pc);
+        if (have) chunk = pc.c0;
+      }
+    };
+    {
+      Piece pc0 = pc;
+      const int idx0 = idx, chunk0 = chunk;
+      const bool have0 = have;
+      int primed = 0;
+      for (; have && primed < stages; ++primed) {
+        feed_w(pc.tile, chunk, primed);
+        advance();
+      }
+      griddep_wait();
+      pc = pc0;
+      idx = idx0;
+      chunk = chunk0;
+      have = have0;
+      for (int s = 0; s < primed; ++s) {
+        feed_x(chunk, s);
+        advance();
+      }
+    }
+    int stage = 0;        // after a full ring the next stage to fill is 0 again (primed == stages),
+    uint32_t phase = 1;   // now on its second use; with fewer iterations than stages nothing is left
+    bool ok = true;
+    while (ok && have) {
+      if (!mbar_wait_sleepy(&empty_bar[stage], phase ^ 1u, p.status)) {
+        ok = false;
+        break;
+      }
+      feed_w(pc.tile, chunk, stage);
+      feed_x(chunk, stage);
+      advance();
+      if (++stage == stages) {
+        stage = 0;
+        phase ^= 1u;
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-#ifdef RB200_SK_LAG
-    __syncwarp();
-    for (int i = lag_issued < 2 ? lag_issued : 2; i > 0; --i) {
-      if (lane == 0) mbar_arrive(&full_bar[lag_stage]);
-      if (++lag_stage == stages) lag_stage = 0;
-    }
-#endif
     return;
   }
 
@@ -333,6 +334,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
 
   int stage = 0;
   uint32_t phase = 0;
+  const uint8_t* sbase = smem;
   bool ok = true;
   Piece pc;
 
@@ -365,8 +367,6 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
   for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, pc); ++idx) {
     const int blk = pc.tile * kConsumerWarps + warp;
     const bool active = blk < n_blocks;
-    const int nblk = min(kConsumerWarps, n_blocks - pc.tile * kConsumerWarps);
-    (void)nblk;
 #pragma unroll
     for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -390,6 +390,98 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
     };
     if (pc.c0 < pc.c1) fetch_global(pc.c0, s_nxt, z_nxt);
 
+    // One stage of this warp's row block.  `full` (a compile-time tag): all four k-blocks of
+    // the chunk exist, so the unrolled body carries no test; the ragged last chunk of a k that
+    // is not a multiple of the chunk takes the tested copy.
+    auto consume = [&](auto full, int nkb) {
+      constexpr bool kFull = decltype(full)::value;
+      const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * ((kFull ? kBlocksPerChunk : nkb) * kTileBytes)) + unit;
+      const uint8_t* xsm = sbase + G::kWBytes + g * G::kXPitch + t * (G::kFrag / 2);
+      uint4 nk_s_g, nk_s_g8, nk_z_g, nk_z_g8;
+      if (SRC == kSrcSmemNK) {
+        const uint4* sp = reinterpret_cast<const uint4*>(sbase + L::kSOff) + warp * 16 + g;
+        nk_s_g = sp[0];
+        nk_s_g8 = sp[8];
+        if (ZMODE == kZeroGeneral && pp.has_z_tile) {
+          const uint4* zp = reinterpret_cast<const uint4*>(sbase + L::kZOff) + warp * 16 + g;
+          nk_z_g = zp[0];
+          nk_z_g8 = zp[8];
+        }
+      }
+#pragma unroll
+      for (int kb = 0; kb < kBlocksPerChunk; ++kb) {
+        if (kFull || kb < nkb) {
+          const uint4 wv = wsm[kb * 32];
+          uint32_t s_g, s_g8, z_g = zconst_h2, z_g8 = zconst_h2;
+          if (SRC == kSrcGlobal) {
+            constexpr int si_div = SP::kSpan / G::kFrag;
+            const uint32_t sp = s_cur[kb / si_div];
+            s_g = prmt(sp, sp, 0x1010u);
+            s_g8 = prmt(sp, sp, 0x3232u);
+            if (ZMODE == kZeroGeneral && p.z) {
+              const uint32_t zp = z_cur[kb / si_div];
+              z_g = prmt(zp, zp, 0x1010u);
+              z_g8 = prmt(zp, zp, 0x3232u);
+            }
+          } else if (SRC == kSrcSmemNK) {
+            const uint32_t a = kb == 0 ? nk_s_g.x : (kb == 1 ? nk_s_g.y : (kb == 2 ? nk_s_g.z : nk_s_g.w));
+            const uint32_t b = kb == 0 ? nk_s_g8.x : (kb == 1 ? nk_s_g8.y : (kb == 2 ? nk_s_g8.z : nk_s_g8.w));
+            s_g = prmt(a, a, half_sel);
+            s_g8 = prmt(b, b, half_sel);
+            if (ZMODE == kZeroGeneral && pp.has_z_tile) {
+              const uint32_t za = kb == 0 ? nk_z_g.x : (kb == 1 ? nk_z_g.y : (kb == 2 ? nk_z_g.z : nk_z_g.w));
+              const uint32_t zb = kb == 0 ? nk_z_g8.x : (kb == 1 ? nk_z_g8.y : (kb == 2 ? nk_z_g8.z : nk_z_g8.w));
+              z_g = prmt(za, za, half_sel);
+              z_g8 = prmt(zb, zb, half_sel);
+            }
+          } else {
+            const int gl = (kb * G::kFrag + lane_k) / (GROUP > 0 ? GROUP : 1);
+            const __half* sp = reinterpret_cast<const __half*>(sbase + L::kSOff) + gl * kTileRows + warp * 16 + g;
+            s_g = h2_bcast(sp[0]);
+            s_g8 = h2_bcast(sp[8]);
+            if (ZMODE == kZeroGeneral && pp.has_z_tile) {
+              const __half* zp = reinterpret_cast<const __half*>(sbase + L::kZOff) + gl * kTileRows + warp * 16 + g;
+              z_g = h2_bcast(zp[0]);
+              z_g8 = h2_bcast(zp[8]);
+            }
+          }
+          if (BITS == 4) {
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            uint4 xv[MT][2];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if ((j & 1) == 0) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                  xv[mt][j >> 1] = *reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 128 + (j >> 1) * 16);
+              }
+              uint32_t a[4];
+              decode_int4_word<ZMODE>(ww[j], zc, s_g, s_g8, z_g, z_g8, a);
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) {
+                const uint4& xr = xv[mt][j >> 1];
+                const uint32_t b0 = (j & 1) ? xr.z : xr.x;
+                const uint32_t b1 = (j & 1) ? xr.w : xr.y;
+                mma_16816(acc[mt][j % kChains], a, b0, b1);
+              }
+            }
+          } else {
+            uint4 xv[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+              xv[mt] = *reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 64);
+            uint32_t a[4];
+            decode_int8_pair<ZMODE>(wv.x, wv.y, zc, s_g, s_g8, z_g, z_g8, a);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) mma_16816(acc[mt][0], a, xv[mt].x, xv[mt].y);
+            decode_int8_pair<ZMODE>(wv.z, wv.w, zc, s_g, s_g8, z_g, z_g8, a);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) mma_16816(acc[mt][kChains - 1], a, xv[mt].z, xv[mt].w);
+          }
+        }
+      }
+    };
+
     for (int chunk = pc.c0; chunk < pc.c1; ++chunk) {
       if (SRC == kSrcGlobal) {
 #pragma unroll
@@ -403,111 +495,18 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
         ok = false;
         break;
       }
-      const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
-      const uint8_t* sbase = smem + (size_t)stage * kStage;
-      if (active && !(ablate & 4)) {
-        const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * (nkb * kTileBytes)) + unit;
-        const uint8_t* xsm = sbase + G::kWBytes + g * G::kXPitch + t * (G::kFrag / 2);
-        uint4 nk_s_g, nk_s_g8, nk_z_g, nk_z_g8;
-        if (SRC == kSrcSmemNK) {
-          const uint4* sp = reinterpret_cast<const uint4*>(sbase + L::kSOff) + warp * 16 + g;
-          nk_s_g = sp[0];
-          nk_s_g8 = sp[8];
-          if (ZMODE == kZeroGeneral && pp.has_z_tile) {
-            const uint4* zp = reinterpret_cast<const uint4*>(sbase + L::kZOff) + warp * 16 + g;
-            nk_z_g = zp[0];
-            nk_z_g8 = zp[8];
-          }
-        }
-#pragma unroll
-        for (int kb = 0; kb < kBlocksPerChunk; ++kb) {
-          if (kb < nkb) {
-            const uint4 wv = wsm[kb * 32];
-            uint32_t s_g, s_g8, z_g = zconst_h2, z_g8 = zconst_h2;
-            if (SRC == kSrcGlobal) {
-              constexpr int si_div = SP::kSpan / G::kFrag;
-              const uint32_t sp = s_cur[kb / si_div];
-              s_g = prmt(sp, sp, 0x1010u);
-              s_g8 = prmt(sp, sp, 0x3232u);
-              if (ZMODE == kZeroGeneral && p.z) {
-                const uint32_t zp = z_cur[kb / si_div];
-                z_g = prmt(zp, zp, 0x1010u);
-                z_g8 = prmt(zp, zp, 0x3232u);
-              }
-            } else if (SRC == kSrcSmemNK) {
-              const uint32_t a = kb == 0 ? nk_s_g.x : (kb == 1 ? nk_s_g.y : (kb == 2 ? nk_s_g.z : nk_s_g.w));
-              const uint32_t b = kb == 0 ? nk_s_g8.x : (kb == 1 ? nk_s_g8.y : (kb == 2 ? nk_s_g8.z : nk_s_g8.w));
-              s_g = prmt(a, a, half_sel);
-              s_g8 = prmt(b, b, half_sel);
-              if (ZMODE == kZeroGeneral && pp.has_z_tile) {
-                const uint32_t za = kb == 0 ? nk_z_g.x : (kb == 1 ? nk_z_g.y : (kb == 2 ? nk_z_g.z : nk_z_g.w));
-                const uint32_t zb = kb == 0 ? nk_z_g8.x : (kb == 1 ? nk_z_g8.y : (kb == 2 ? nk_z_g8.z : nk_z_g8.w));
-                z_g = prmt(za, za, half_sel);
-                z_g8 = prmt(zb, zb, half_sel);
-              }
-            } else {
-              const int gl = (kb * G::kFrag + lane_k) / (GROUP > 0 ? GROUP : 1);
-              const __half* sp = reinterpret_cast<const __half*>(sbase + L::kSOff) + gl * kTileRows + warp * 16 + g;
-              s_g = h2_bcast(sp[0]);
-              s_g8 = h2_bcast(sp[8]);
-              if (ZMODE == kZeroGeneral && pp.has_z_tile) {
-                const __half* zp = reinterpret_cast<const __half*>(sbase + L::kZOff) + gl * kTileRows + warp * 16 + g;
-                z_g = h2_bcast(zp[0]);
-                z_g8 = h2_bcast(zp[8]);
-              }
-            }
-            if (BITS == 4) {
-              const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-              uint4 xv[MT][2];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if ((j & 1) == 0) {
-#pragma unroll
-                  for (int mt = 0; mt < MT; ++mt)
-                    xv[mt][j >> 1] = *reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 128 + (j >> 1) * 16);
-                }
-                uint32_t a[4];
-                if (ablate & 1) {
-                  a[0] = ww[j]; a[1] = ww[j] ^ s_g; a[2] = ww[j] + s_g8; a[3] = ww[j] | z_g;
-                } else {
-                  decode_int4_word<ZMODE>(ww[j], zc, s_g, s_g8, z_g, z_g8, a);
-                }
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                  const uint4& xr = xv[mt][j >> 1];
-                  const uint32_t b0 = (j & 1) ? xr.z : xr.x;
-                  const uint32_t b1 = (j & 1) ? xr.w : xr.y;
-                  if (ablate & 2) {
-                    acc[mt][j % kChains][0] += __uint_as_float(a[0] ^ b0);
-                    acc[mt][j % kChains][1] += __uint_as_float(a[1] ^ b1);
-                    acc[mt][j % kChains][2] += __uint_as_float(a[2]);
-                    acc[mt][j % kChains][3] += __uint_as_float(a[3]);
-                  } else {
-                    mma_16816(acc[mt][j % kChains], a, b0, b1);
-                  }
-                }
-              }
-            } else {
-              uint4 xv[MT];
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt)
-                xv[mt] = *reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 64);
-              uint32_t a[4];
-              decode_int8_pair<ZMODE>(wv.x, wv.y, zc, s_g, s_g8, z_g, z_g8, a);
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) mma_16816(acc[mt][0], a, xv[mt].x, xv[mt].y);
-              decode_int8_pair<ZMODE>(wv.z, wv.w, zc, s_g, s_g8, z_g, z_g8, a);
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) mma_16816(acc[mt][kChains - 1], a, xv[mt].z, xv[mt].w);
-            }
-          }
-        }
+      if (active) {
+        const int nkb = kb_total - chunk * kBlocksPerChunk;
+        if (nkb >= kBlocksPerChunk) consume(std::true_type{}, kBlocksPerChunk);
+        else consume(std::false_type{}, nkb);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      sbase += kStage;
       if (++stage == stages) {
         stage = 0;
         phase ^= 1u;
+        sbase = smem;
       }
     }
     if (!ok) break;
@@ -537,7 +536,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
 #pragma unroll
           for (int c = 0; c < 4; ++c) head[mt][c] = fin[mt][c];
       } else {
-        float* dst = pp.partial + ((size_t)((blockIdx.x * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
+        float* dst = pp.partial + ((size_t)((cta * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -545,14 +544,14 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
       }
     } else {
       // tail piece: publish for the owner (the CTA that holds this tile's first chunk)
-      float* dst = pp.partial + ((size_t)((blockIdx.x * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
+      float* dst = pp.partial + ((size_t)((cta * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) dst[mt * 128 + c * 32] = fin[mt][c];
       __threadfence();
       __syncwarp();
-      if (lane == 0) st_release_u32(pp.flags + blockIdx.x * kConsumerWarps + warp, pp.epoch);
+      if (lane == 0) st_release_u32(pp.flags + cta * kConsumerWarps + warp, 1u);
     }
   }
 
@@ -560,12 +559,18 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
   if (ok && have_head) {
     const long long hi_it = (long long)head_tile * cpt + cpt - 1;
     const int last_cta = (int)(((hi_it + 1) * grid - 1) / total);
+    const unsigned long long limit_ns = (pp.wait_limit_ms ? (unsigned long long)pp.wait_limit_ms : 2000ull) * 1000000ull;
     bool flags_ok = true;
-    for (int c = blockIdx.x + 1; c <= last_cta && flags_ok; ++c) {
-      int spins = 0;
-      while (ld_acquire_u32(pp.flags + c * kConsumerWarps + warp) != pp.epoch) {
+    for (int c = cta + 1; c <= last_cta && flags_ok; ++c) {
+      const unsigned* f = pp.flags + c * kConsumerWarps + warp;
+      if (ld_acquire_u32(f) != 0u) continue;
+      unsigned long long t0;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+      while (ld_acquire_u32(f) == 0u) {
         __nanosleep(64);
-        if (++spins > (1 << 22)) {  // several seconds: give up, report, leave the tile unwritten
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > limit_ns) {  // give up, report, leave the tile unwritten
           if (p.status) atomicExch(p.status, kStatusWaitTimeout);
           flags_ok = false;
           break;
@@ -581,19 +586,24 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? RB200_SK_CTAS_MT1 : 2) gem
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) sum[mt][cc] = head[kHeadInRegs ? mt : 0][cc];
       } else {
-        const float* own = pp.partial + ((size_t)((blockIdx.x * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
+        const float* own = pp.partial + ((size_t)((cta * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) sum[mt][cc] = own[mt * 128 + cc * 32];  // written by this same thread
       }
-      for (int c = blockIdx.x + 1; c <= last_cta; ++c) {  // fixed CTA order: deterministic
+      for (int c = cta + 1; c <= last_cta; ++c) {  // fixed CTA order: deterministic
         const float* src = pp.partial + ((size_t)((c * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) sum[mt][cc] += __ldcg(src + mt * 128 + cc * 32);
       }
+      // every slot has exactly one consumer (this warp): hand the flags back at rest.  The
+      // next launch writes them only after this grid has completed.
+      __syncwarp();
+      if (lane == 0)
+        for (int c = cta + 1; c <= last_cta; ++c) pp.flags[c * kConsumerWarps + warp] = 0u;
       store_tile(sum, head_tile);
     }
   }
@@ -611,9 +621,9 @@ int launch_sk_i8(const Params& pp, const Launch& l, cudaStream_t stream);
 
 }  // namespace sk
 
-// Host entry: plans and launches the stream-k decode kernel.  `partial` / `flags` are scratch
-// (flags must start at zero and are compared with the per-launch `epoch`).
+// Host entry: plans and launches the stream-k decode kernel.  `partial` / `flags` are scratch;
+// the flags must be zero before the first launch and are left zero by every launch.
 int gemv_sk_run(const GemvParams& p, int bits, int zmode, int sm_count, float* partial, size_t partial_bytes,
-                unsigned* flags, size_t flag_count, unsigned epoch, cudaStream_t stream);
+                unsigned* flags, size_t flag_count, cudaStream_t stream);
 
 }  // namespace rb200

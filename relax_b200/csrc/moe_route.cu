@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__
 
 int blocks_for(int64_t work, int threads) {
   int64_t b = (work + threads - 1) / threads;
-  if (b > 148 * 16) b = 148 * 16;
+  if (b > (int64_t)sm_count_current() * 16) b = (int64_t)sm_count_current() * 16;
   if (b < 1) b = 1;
   return (int)b;
 }

@@ -62,6 +62,28 @@ int setup_current_device(PerDevice** out) {
 bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
+
+// The status word of the static array on the current device, for rb200_check_async_error: read
+// (and cleared when set) with plain copies, so asking never allocates.  0 when the no-alloc entry
+// has not run on this device.
+int noalloc_read_status(int* status_out) {
+  *status_out = 0;
+  int dev = -1;
+  RB200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return 0;
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    base = g_per_device[dev].base;
+  }
+  if (!base) return 0;
+  int v = 0;
+  RB200_CUDA(cudaMemcpy(&v, base, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0) RB200_CUDA(cudaMemset(base, 0, sizeof(int)));
+  *status_out = v;
+  return 0;
+}
+
 }  // namespace rb200
 
 using namespace rb200;
@@ -89,6 +111,15 @@ extern "C" int rb200_gemm_fp16_intx_noalloc(const rb200_gemm_desc* d, void* stre
   const int64_t ldo = d->ldo > 0 ? d->ldo : d->n;
   RB200_CHECK(is_aligned16(d->x) && is_aligned16(d->w) && ldx % 8 == 0,
               "x and w must be 16-byte aligned with ldx %% 8 == 0");
+  RB200_CHECK(d->activation != RB200_ACT_SWIGLU,
+              "rb200_gemm_fp16_intx_noalloc has no fused gate/up form: run the plain matmul and gate afterwards, "
+              "or use rb200_gemm_fp16_intx");
+  RB200_CHECK(d->activation >= RB200_ACT_IDENTITY && d->activation <= RB200_ACT_GELU, "unknown activation code %d",
+              d->activation);
+  RB200_CHECK(d->binary_op >= RB200_BIN_NONE && d->binary_op <= RB200_BIN_MULTIPLY, "unknown binary_op code %d",
+              d->binary_op);
+  RB200_CHECK(d->unary_op >= RB200_UN_IDENTITY && d->unary_op <= RB200_UN_RELU, "unknown unary_op code %d",
+              d->unary_op);
   RB200_CHECK(d->binary_op == RB200_BIN_NONE || d->residual, "binary_op needs a residual tensor");
   RB200_CHECK(d->bias_stride == 0 || d->bias_stride == d->n, "bias_stride must be 0 or n");
   const int group = (d->group_size <= 0 || d->group_size >= d->k) ? 0 : (int)d->group_size;
@@ -109,8 +140,10 @@ extern "C" int rb200_gemm_fp16_intx_noalloc(const rb200_gemm_desc* d, void* stre
               plan.partial_bytes, kPartialBytes);
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  // The array keeps whatever the previous call left: tickets and status must start at zero.
-  RB200_CUDA(cudaMemsetAsync(pd->base, 0, kHeaderBytes + kCounterBytes, stream));
+  // The array keeps whatever the previous call left: the tickets must start at zero.  The status
+  // word is left alone - a wait that gave up in an earlier call stays visible until
+  // rb200_check_async_error reads and clears it.
+  RB200_CUDA(cudaMemsetAsync(pd->base + kHeaderBytes, 0, kCounterBytes, stream));
 
   int zmode = kZeroGeneral;
   if (!d->zeros) {

@@ -185,15 +185,91 @@ int preprocess_common(const char* fn, const DLTensor* w, const DLTensor* out, bo
   return rc;
 }
 
+// A tensor this library allocated for a caller: DLPack's managed form, freed through its deleter.
+struct OwnedTensor {
+  DLManagedTensor mt;
+  int64_t shape[8];
+};
+void owned_tensor_deleter(DLManagedTensor* self) {
+  if (!self) return;
+  OwnedTensor* o = static_cast<OwnedTensor*>(self->manager_ctx);
+  if (o->mt.dl_tensor.device.device_type == kDLCUDA) cudaFree(o->mt.dl_tensor.data);
+  else free(o->mt.dl_tensor.data);
+  delete o;
+}
+// New compact tensor with the shape, dtype and device of `like` (CUDA: cudaMalloc on that device,
+// which must be current; CPU: malloc).
+int alloc_like(const char* fn, const DLTensor* like, OwnedTensor** out) {
+  PF_CHECK(like->ndim >= 1 && like->ndim <= 8, "%s: rank %d not supported", fn, like->ndim);
+  OwnedTensor* o = new OwnedTensor();
+  memset(&o->mt, 0, sizeof(o->mt));
+  size_t bytes = (size_t)((like->dtype.bits * like->dtype.lanes + 7) / 8);
+  for (int i = 0; i < like->ndim; ++i) {
+    o->shape[i] = like->shape[i];
+    bytes *= (size_t)like->shape[i];
+  }
+  void* data = nullptr;
+  if (like->device.device_type == kDLCUDA) {
+    cudaError_t e = cudaMalloc(&data, bytes ? bytes : 1);
+    if (e != cudaSuccess) {
+      delete o;
+      rb200::set_last_error("%s: cudaMalloc(%zu) for the result failed: %s", fn, bytes, cudaGetErrorString(e));
+      return -1;
+    }
+  } else {
+    data = malloc(bytes ? bytes : 1);
+    if (!data) {
+      delete o;
+      rb200::set_last_error("%s: malloc(%zu) for the result failed", fn, bytes);
+      return -1;
+    }
+  }
+  o->mt.dl_tensor.data = data;
+  o->mt.dl_tensor.device = like->device;
+  o->mt.dl_tensor.ndim = like->ndim;
+  o->mt.dl_tensor.dtype = like->dtype;
+  o->mt.dl_tensor.shape = o->shape;
+  o->mt.dl_tensor.strides = nullptr;
+  o->mt.dl_tensor.byte_offset = 0;
+  o->mt.manager_ctx = o;
+  o->mt.deleter = owned_tensor_deleter;
+  *out = o;
+  return 0;
+}
+
+// Two calling forms.  (packed_weight, sm, is_int4): the reference's own argument list
+// (src/runtime/contrib/cutlass/weight_preprocess.cc:38-39); the result is allocated here on the
+// input's device and returned as a DLManagedTensor* (type code: opaque handle) that the caller
+// releases through its deleter - a standalone library cannot mint the reference runtime's NDArray
+// object, DLPack's managed tensor is the form every such runtime can adopt without a copy.
+// (packed_weight, sm, is_int4, out): destination-passing, nothing allocated, nothing returned.
 int pf_ft_preprocess_weight(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
   Args a{v, tc, n, "cutlass.ft_preprocess_weight"};
   const DLTensor *w, *out;
   int64_t sm, is_int4;
-  PF_CHECK(n == 4, "%s expects (packed_weight, sm, is_int4, out), got %d arguments", a.fname, n);
-  if (a.tensor(0, &w) || a.integer(1, &sm) || a.integer(2, &is_int4) || a.tensor(3, &out)) return -1;
+  PF_CHECK(n == 3 || n == 4, "%s expects (packed_weight, sm, is_int4[, out]), got %d arguments", a.fname, n);
+  if (a.tensor(0, &w) || a.integer(1, &sm) || a.integer(2, &is_int4)) return -1;
   PF_CHECK(sm >= 70 && sm <= 120, "%s: implausible sm=%lld", a.fname, (long long)sm);
-  if (ret_tc) *ret_tc = RB200_ARG_NULL;
-  return preprocess_common(a.fname, w, out, is_int4 != 0, RB200_LAYOUT_FT_KN);
+  if (n == 4) {
+    if (a.tensor(3, &out)) return -1;
+    if (ret_tc) *ret_tc = RB200_ARG_NULL;
+    return preprocess_common(a.fname, w, out, is_int4 != 0, RB200_LAYOUT_FT_KN);
+  }
+  if (w->device.device_type == kDLCUDA) {
+    int dev = -1;
+    cudaGetDevice(&dev);
+    PF_CHECK(dev == w->device.device_id, "%s: packed_weight is on cuda:%d but the current device is cuda:%d", a.fname,
+             w->device.device_id, dev);
+  }
+  OwnedTensor* o = nullptr;
+  if (alloc_like(a.fname, w, &o)) return -1;
+  if (preprocess_common(a.fname, w, &o->mt.dl_tensor, is_int4 != 0, RB200_LAYOUT_FT_KN) != 0) {
+    owned_tensor_deleter(&o->mt);
+    return -1;
+  }
+  if (ret) ret->v_handle = &o->mt;
+  if (ret_tc) *ret_tc = RB200_ARG_HANDLE;
+  return 0;
 }
 
 int pf_preprocess_q4f16(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
@@ -311,8 +387,13 @@ int ft_gemm(const char* fname, int bits, RB200Value* v, int* tc, int n_args, int
   PF_CHECK(numel(out) == m * n, "%s: out has %lld elements, expected m*n=%lld", fname,
            (long long)numel(out), (long long)(m * n));
   const bool per_col = group <= 0 || group >= k;
-  PF_CHECK(numel(s) == (per_col ? n : (k / group) * n), "%s: scales have %lld elements, expected %lld",
-           fname, (long long)numel(s), (long long)(per_col ? n : (k / group) * n));
+  // the shapes the reference's pattern check admits (python/tvm/relax/backend/contrib/cutlass.py:255-257):
+  // (N,), (1, N) or (K / group_size, N)
+  PF_CHECK(s->ndim >= 1 && s->ndim <= 2 && s->shape[s->ndim - 1] == n,
+           "%s: scales must be [n], [1, n] or [k / group_size, n]", fname);
+  PF_CHECK(s->ndim == 1 || s->shape[0] == (per_col ? 1 : k / group),
+           "%s: scales have %lld rows, expected %lld", fname, (long long)s->shape[0],
+           (long long)(per_col ? 1 : k / group));
   const char* a_name = act;
   rb200_gemm_desc d;
   memset(&d, 0, sizeof(d));

@@ -144,7 +144,7 @@ int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, in
   const int64_t total = units * experts;
   const int threads = 256;
   int64_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > (int64_t)sm_count_current() * 32) blocks = (int64_t)sm_count_current() * 32;
   if (blocks == 0) return 0;
   const uint8_t* s = static_cast<const uint8_t*>(src);
   uint8_t* d = static_cast<uint8_t*>(dst);
@@ -166,7 +166,7 @@ int interleave_rows_launch(const void* src, void* dst, int64_t outer, int64_t n,
   const int64_t total = outer * n * inner;
   if (total == 0) return 0;
   int64_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (int64_t)sm_count_current() * 16) blocks = (int64_t)sm_count_current() * 16;
   interleave_rows_kernel<<<(int)blocks, 256, 0, stream>>>(static_cast<const __half*>(src), static_cast<__half*>(dst),
                                                          outer, n, inner);
   RB200_CUDA(cudaGetLastError());
@@ -177,7 +177,7 @@ int unpack_zeros_autogptq_launch(const void* zq, void* out, int64_t groups, int6
   const int64_t total = groups * n;
   if (total == 0) return 0;
   int64_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (int64_t)sm_count_current() * 16) blocks = (int64_t)sm_count_current() * 16;
   unpack_zeros_autogptq_kernel<<<(int)blocks, 256, 0, stream>>>(static_cast<const uint32_t*>(zq),
                                                                static_cast<__half*>(out), total, n);
   RB200_CUDA(cudaGetLastError());

@@ -8,9 +8,6 @@
 
 namespace rb200 {
 
-// RB200_GEMM_SPLIT_K=n asks for n splits (1: never split)
-static constexpr bool kSplitKByDefault = true;
-
 static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count, const int64_t* indptr,
                       int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, bool grouped,
                       cudaStream_t stream) {
@@ -24,8 +21,6 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
                 "(n=%d, k=%d)", p_in.n, p_in.k);
     return 1;
   }
-  static const bool disabled = getenv("RB200_GEMM_NO_TCGEN05") != nullptr;
-  if (disabled && !grouped) return 1;
   RB200_CHECK(num_experts >= 1 && num_experts <= kMaxExperts, "num_experts=%d outside [1, %d]", num_experts,
               kMaxExperts);
 
@@ -71,19 +66,15 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
     RB200_CHECK(p.s_n != 0 && s_expert_stride % p.s_n == 0, "expert stride of the scales must be a multiple of their row stride");
   }
 
-  static const int env_grid = getenv("RB200_GEMM_GRID") ? atoi(getenv("RB200_GEMM_GRID")) : 0;
-  static const int env_split = getenv("RB200_GEMM_SPLIT_K") ? atoi(getenv("RB200_GEMM_SPLIT_K")) : 0;
   long long grid = sm_count;  // one persistent CTA per SM (a tensor-memory kernel gets occupancy 1)
-  if (env_grid > 0) grid = env_grid;
   pp.k_splits = 1;
   if (!grouped) {
     const long long tiles = (long long)(p.n / kTileRows) * ((p.m + pp.nb - 1) / pp.nb);
     // fewer tiles than half the SMs: cut k, in whole weight stages, so that the idle SMs take part
     const int kb_total = p.k / kKBlock;
     const int blocks_per_chunk = bits == 16 ? 1 : (bits == 4 ? 4 : 2);
-    int split = kSplitKByDefault ? (int)(sm_count / tiles) : 1;
+    int split = (int)(sm_count / tiles);
     if (split > 8) split = 8;
-    if (env_split > 0) split = env_split;
     if (split > sm_count / tiles) split = (int)(sm_count / tiles);
     const int chunks = (kb_total + blocks_per_chunk - 1) / blocks_per_chunk;
     while (split > 1 && chunks / split * blocks_per_chunk < 8) --split;  // every split at least 8 MMA blocks
@@ -102,8 +93,6 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
   const size_t budget = (size_t)227 * 1024;
   int xs = kMaxXStages;
   while (xs > 2 && smem_bytes(pp.nb, xs) > budget) --xs;
-  static const int env_xs = getenv("RB200_GEMM_X_STAGES") ? atoi(getenv("RB200_GEMM_X_STAGES")) : 0;
-  if (env_xs >= 2 && env_xs <= xs) xs = env_xs;
   pp.x_stages = xs;
   l.smem = smem_bytes(pp.nb, xs);
 

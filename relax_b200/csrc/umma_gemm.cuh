@@ -33,7 +33,7 @@
 #include "dequant.cuh"
 #include "gemv.h"
 #include "gemv_cluster.cuh"
-#include "umma_gemv.cuh"
+#include "umma_common.cuh"
 
 namespace rb200 {
 namespace um {
@@ -48,10 +48,7 @@ constexpr int kScaleBoxBytes = 2048;
 constexpr int kWStageBytes = kWBytes + 2 * kScaleBoxBytes;
 constexpr int kWStages = 3;
 constexpr int kMaxXStages = 8;
-#ifndef RB200_UM_NUMA
-#define RB200_UM_NUMA 4
-#endif
-constexpr int kNumA = RB200_UM_NUMA;        // TMEM A buffers of 32 columns (one 64-k block each)
+constexpr int kNumA = 4;                    // TMEM A buffers of 32 columns (one 64-k block each)
 constexpr int kTmemCols = 512;
 constexpr int kDCols = 256;                 // accumulator: columns [0, 256); A buffers follow
 constexpr int kMaxNb = 256;
@@ -87,11 +84,7 @@ inline size_t smem_bytes(int nb, int x_stages) {
 
 // hand-offs on the critical path (A buffers, x stages)
 __device__ __forceinline__ bool um_wait(uint64_t* bar, uint32_t parity, int* status) {
-#ifdef RB200_UM_SPIN
-  return mbar_wait_bounded(bar, parity, status);
-#else
   return mbar_wait_parked(bar, parity, status);
-#endif
 }
 
 using gc::tma_load_2d;
@@ -196,11 +189,11 @@ __device__ __forceinline__ Tile get_tile(const TileTables& tt, int num_experts, 
 }
 
 template <int BITS, int ZMODE, int GROUP, int SRC, int HI>
-__device__ __forceinline__ void decode_any(int kbm, const GemvParams& p, const ug::Params& up, const RowCtx& c,
+__device__ __forceinline__ void decode_any(int kbm, const GemvParams& p, bool has_z_tile, const RowCtx& c,
                                            const ZeroConsts& zc, uint32_t zconst_h2, int group,
                                            uint32_t (&regs)[32]) {
   if constexpr (BITS == 4) {
-    ug::decode_block_kb<ZMODE, GROUP, SRC, HI>(kbm, p, up, c, zc, zconst_h2, group, regs);
+    ug::decode_block_kb<ZMODE, GROUP, SRC, HI>(kbm, p, has_z_tile, c, zc, zconst_h2, group, regs);
   } else {
     if (kbm == 0) decode_block8<ZMODE, GROUP, HI, 0>(p, c, zc, zconst_h2, group, regs);
     else decode_block8<ZMODE, GROUP, HI, 1>(p, c, zc, zconst_h2, group, regs);
@@ -304,21 +297,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto ch_lo = [&](int sp) { return (int)((long long)sp * chunks / S); };
   auto kb_lo = [&](int sp) { return min(ch_lo(sp) * kBlocksPerChunk, kb_total); };
   bool ok = true;
-#ifdef RB200_ABLATE
-  const int ablate = p.ablate;
-  unsigned long long* tl = (blockIdx.x == 0 && (ablate & 65536) && p.partial) ? reinterpret_cast<unsigned long long*>(p.partial) + (1 << 18) : nullptr;
-#define RB200_GTL(role, i)                                                         \
-  do {                                                                             \
-    if (tl && (i) < 64) {                                                          \
-      unsigned long long t_;                                                       \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                        \
-      tl[(role) * 64 + (i)] = t_;                                                  \
-    }                                                                              \
-  } while (0)
-#else
-  constexpr int ablate = 0;
-#define RB200_GTL(role, i) do {} while (0)
-#endif
 
   if (warp == 0) {
     // ============================================================ producer: packed weights
@@ -365,15 +343,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       (void)ws;
       (void)wph;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_i) {
-        RB200_GTL(0, (int)tile_i);
-#ifdef RB200_ABLATE
-        if (tl && tile_i < 32) tl[9 * 64 + tile_i] = (unsigned long long)clock64();
-#endif
         if (!mbar_wait_parked(d_empty, (tile_i & 1u) ^ 1u, p.status)) {
           ok = false;
           break;
         }
-        RB200_GTL(1, (int)tile_i);
         tc_fence_after();
         const int kb_first = kb_lo(t % S), kb_end = kb_lo(t % S + 1);
         for (int kb = kb_first; kb < kb_end; ++kb, ++q) {
@@ -392,7 +365,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           tc_fence_after();
-          if (kb == kb_first) RB200_GTL(2, (int)tile_i);
           const uint32_t xbase = smem_u32(x_ring + (size_t)xs * x_stage_bytes);
           if (kDense) {
             const uint32_t wbase = smem_u32(w_ring + (size_t)ws * kWStageBytes);
@@ -409,8 +381,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t a_tmem = a_col0 + ab * 32;
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              if (!(ablate & 8))
-                tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == kb_first && j == 0) ? 0u : 1u);
+              tc_mma_ts(d_col0, a_tmem + j * 8, make_b_desc(xbase + j * 32), idesc, (kb == kb_first && j == 0) ? 0u : 1u);
             tc_commit(&a_empty[ab]);
           }
           tc_commit(&x_empty[xs]);
@@ -420,7 +391,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         if (ok) tc_commit(d_full);
-        RB200_GTL(3, (int)tile_i);
       }
     }
   } else if (warp == 2) {
@@ -485,9 +455,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = false;
           break;
         }
-        if (lane == 0 && (ablate & 1)) {
-          mbar_arrive(&x_full[xs]);
-        } else if (lane == 0) {
+        if (lane == 0) {
           mbar_arrive_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
           tma_load_2d(x_ring + (size_t)xs * x_stage_bytes, &tmap_x, kb * kKBlock, m0, &x_full[xs]);
         }
@@ -516,8 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t unit_off[4];
 #pragma unroll
     for (int t = 0; t < 4; ++t) unit_off[t] = (uint32_t)(t * 128 + ((g + 2 * t) & 7) * 16);
-    ug::Params up;  // the int4 block decoder reads only has_z_tile from it
-    up.has_z_tile = pp.has_z_tile;
+    const bool has_z_tile = pp.has_z_tile != 0;
 
     int ws = 0;
     uint32_t wph = 0;
@@ -537,7 +504,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         s_chan = h2_bcast(p.s[n_row_s * p.s_n]);
         if (ZMODE == kZeroGeneral && p.z) z_chan = h2_bcast(p.z[n_row_s * p.s_n]);
       }
-      if (dw == 0 && lane == 0) RB200_GTL(4, (int)tile_i);
       for (int chunk = ch_lo(split); chunk < (kDense ? 0 : ch_lo(split + 1)) && ok; ++chunk) {
         if (!mbar_wait_parked(&w_full[ws], wph, p.status)) {
           ok = false;
@@ -573,11 +539,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           tc_fence_after();
           uint32_t regs[32];
-          if (ablate & 2) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) regs[i] = 0x3c003c00u;
-          } else if (hi) decode_any<BITS, ZMODE, GROUP, SRC, 1>(kbm, p, up, c, zc, zconst_h2, group, regs);
-          else decode_any<BITS, ZMODE, GROUP, SRC, 0>(kbm, p, up, c, zc, zconst_h2, group, regs);
+          if (hi) decode_any<BITS, ZMODE, GROUP, SRC, 1>(kbm, p, has_z_tile, c, zc, zconst_h2, group, regs);
+          else decode_any<BITS, ZMODE, GROUP, SRC, 0>(kbm, p, has_z_tile, c, zc, zconst_h2, group, regs);
           tc_st32(lane_taddr | (a_col0 + ab * 32), regs);
           tc_wait_st();
           tc_fence_before();
@@ -594,12 +557,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) break;
       // ---------------------------------------------------------- epilogue of this tile
-      if (dw == 0 && lane == 0) RB200_GTL(5, (int)tile_i);
       if (!mbar_wait_parked(d_full, tile_i & 1u, p.status)) {
         ok = false;
         break;
       }
-      if (dw == 0 && lane == 0) RB200_GTL(6, (int)tile_i);
       tc_fence_after();
       const int64_t m0 = tile.m0;
       const int64_t m_end = tile.m_end;
@@ -641,10 +602,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (reduce_here) __threadfence();
       }
       for (int c0 = c_begin; reduce_here && c0 < c_end; c0 += 16, ++estep) {
-        if (m0 + c0 >= m_end || (ablate & 4)) break;
+        if (m0 + c0 >= m_end) break;
         float v[16];
-        const int es_ = (c0 - c_begin) / 16;
-        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5);
         tc_ld16(lane_taddr | (d_col0 + c0), v);
         if (SPLITK && S > 1) {
           // all splits in split order, this CTA's own part straight from tensor memory
@@ -664,7 +623,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = acc[i];
         }
-        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 1);
         // transpose through shared memory: 16 batch rows x 128 weight rows of fp16 (rounded once,
         // after the epilogue), so that global stores are whole 256-byte row segments
         __half* st = e_stage + ((grp * 2 + (estep & 1u)) * 16) * kTileRows;
@@ -672,13 +630,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 16; ++i) st[i * kTileRows + row] = __float2half_rn(v[i]);
         __syncwarp();
-        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 2);
         if (lane == 0) mbar_arrive(&e_bar[grp]);
         if (!mbar_wait_parked(&e_bar[grp], estep & 1u, p.status)) {
           ok = false;
           break;
         }
-        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 3);
 #pragma unroll
         for (int pass = 0; pass < 2; ++pass) {
           const int mi = pass * 8 + (gj >> 4), ch = gj & 15;
@@ -705,10 +661,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 *reinterpret_cast<const uint4*>(st + mi * kTileRows + ch * 8);
           }
         }
-        if (dw == 0 && lane == 0 && tile_i == 1) RB200_GTL(8, es_ * 5 + 4);
       }
       if (!ok) break;
-      if (dw == 0 && lane == 0) RB200_GTL(7, (int)tile_i);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(d_empty);

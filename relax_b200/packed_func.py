@@ -156,10 +156,28 @@ _ALLOCATING = {"cutlass.ft_preprocess_weight", "relax_b200.preprocess_weight_q4f
 _CACHE = {}
 
 
-def get_global_func(name: str, allow_missing: bool = False):
+def adopt_managed_tensor(handle: int) -> torch.Tensor:
+    """Turns a ``DLManagedTensor*`` returned by a PackedFunc (the allocating form of
+    ``cutlass.ft_preprocess_weight``) into a torch tensor without a copy; torch calls the
+    tensor's deleter when the last reference goes away."""
+    new_capsule = ctypes.pythonapi.PyCapsule_New
+    new_capsule.restype = ctypes.py_object
+    new_capsule.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p]
+    return torch.utils.dlpack.from_dlpack(new_capsule(handle, b"dltensor", None))
+
+
+def get_global_func(name: str, allow_missing: bool = False, raw: bool = False):
     """``tvm.get_global_func`` counterpart.  Destination-passing operators are returned as is;
     the preprocess functions are wrapped so that they allocate and return their result, like the
-    reference's."""
+    reference's.  ``raw=True`` returns the registered function itself (what a C host gets from
+    ``RB200FuncGetGlobal``), without that wrapper."""
+    if raw:
+        lib = _lib.load()
+        h = ctypes.c_void_p()
+        _lib.check(lib.RB200FuncGetGlobal(name.encode(), ctypes.byref(h)))
+        if not h.value:
+            raise ValueError("Cannot find global function %s" % name)
+        return PackedFunc(name, h.value)
     hit = _CACHE.get(name)
     if hit is not None:
         return hit

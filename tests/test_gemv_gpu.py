@@ -132,13 +132,6 @@ def test_gemv_config0_full(oracle):
     assert_close(got, exp)
 
 
-@pytest.mark.parametrize("name,m", [("qkv", 1), ("o", 8), ("gate_up", 32), ("down", 1), ("down", 32)])
-def test_gemv_llama7b_linears(oracle, name, m):
-    case = synth.config1(name, m)
-    got, exp = _run_q4(oracle, case)
-    assert_close(got, exp)
-
-
 @pytest.mark.parametrize("group,asym", [(64, False), (128, False), (128, True), (512, False), (16, True), (96, False)])
 def test_gemv_q4_groups_and_zero_points(oracle, group, asym):
     k = 1536

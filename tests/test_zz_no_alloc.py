@@ -65,10 +65,58 @@ def test_noalloc_matches_regular_entry_twice_in_a_row(oracle, m, k, n, group, as
         outs.append(out)
     # the entry point itself is deterministic: leftovers of the first call change nothing
     assert torch.equal(outs[0], outs[1])
-    # and both agree with the CPU oracle
+    # and each of them agrees with the CPU oracle directly
     C = oracle.C()
     wq = C.decode_q4_nk(case.w, case.scales, case.zeros, 7.0, group)
-    assert_close(ref.cpu().numpy(), C.epilogue(C.matmul_f32(case.x, wq)))
+    exp = C.epilogue(C.matmul_f32(case.x, wq))
+    assert_close(outs[0].cpu().numpy(), exp)
+    assert_close(ref.cpu().numpy(), exp)
+    # no bounded wait gave up; asking allocates nothing either
+    st = ctypes.c_int(-1)
+    assert lib.rb200_check_async_error(None, ctypes.byref(st)) == 0 and st.value == 0
+
+
+def test_noalloc_epilogue_matches_oracle(oracle):
+    """bias + silu + residual (multiply) + relu through the allocation-free entry."""
+    lib = _lib.load()
+    m, k, n = 6, 1024, 512
+    case = synth.q4_case(np.random.Generator(np.random.PCG64(99)), m, k, n, 32)
+    rs = np.random.RandomState(5)
+    bias = rs.randn(n).astype(np.float16)
+    res = rs.randn(m, n).astype(np.float16)
+    x = torch.from_numpy(case.x).cuda()
+    s = torch.from_numpy(case.scales).cuda()
+    pre = ops.preprocess_weight_q4f16(torch.from_numpy(case.w.view(np.int32)).cuda())
+    bd, rd = torch.from_numpy(bias).cuda(), torch.from_numpy(res).cuda()
+    out = torch.empty(m, n, dtype=torch.float16, device="cuda")
+    d = _desc(x, pre, s, out, 32)
+    d.bias, d.residual = bd.data_ptr(), rd.data_ptr()
+    d.activation, d.binary_op, d.unary_op = 2, 2, 1  # silu, multiply, relu
+    for _ in range(2):
+        _call(lib.rb200_gemm_fp16_intx_noalloc, d)
+    torch.cuda.synchronize()
+    C = oracle.C()
+    exp = C.epilogue(C.matmul_f32(case.x, C.decode_q4_nk(case.w, case.scales, None, 7.0, 32)), bias, res, "silu",
+                     "multiply", "relu")
+    assert_close(out.cpu().numpy(), exp, tight=False)
+
+
+def test_noalloc_refuses_the_fused_gate_up_form_and_unknown_codes(oracle):
+    lib = _lib.load()
+    case = synth.q4_case(np.random.Generator(np.random.PCG64(2)), 4, 256, 64, 32)
+    x = torch.from_numpy(case.x).cuda()
+    s = torch.from_numpy(case.scales).cuda()
+    pre = ops.preprocess_weight_q4f16(torch.from_numpy(case.w.view(np.int32)).cuda())
+    out = torch.empty(4, 64, dtype=torch.float16, device="cuda")
+    d = _desc(x, pre, s, out, 32)
+    d.activation = 4  # RB200_ACT_SWIGLU
+    with pytest.raises(relax_b200.RB200Error, match="gate/up"):
+        _call(lib.rb200_gemm_fp16_intx_noalloc, d)
+    for field in ("activation", "binary_op", "unary_op"):
+        d = _desc(x, pre, s, out, 32)
+        setattr(d, field, 9)
+        with pytest.raises(relax_b200.RB200Error, match="unknown"):
+            _call(lib.rb200_gemm_fp16_intx_noalloc, d)
 
 
 def test_noalloc_rejects_sizes_beyond_its_fixed_scratch(oracle):
