@@ -10,7 +10,7 @@ import argparse
 
 import torch
 
-from . import ops
+import sys; sys.path.insert(0, "/root/repo"); from relax_b200 import ops
 
 
 def main():

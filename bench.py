@@ -38,14 +38,38 @@ GROUP = 32
 WEIGHT_SETS = 4  # rotated so that a weight is evicted from the 126 MB L2 before it is reused
 
 
+def _synth():
+    """The synthetic-input module, loaded by path: importing the package would load the CUDA
+    library, which the CPU arm must not touch."""
+    import importlib.util
+    mod = sys.modules.get("_rb200_synth")
+    if mod is None:
+        spec = importlib.util.spec_from_file_location("_rb200_synth", os.path.join(ROOT, "relax_b200", "synth.py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["_rb200_synth"] = mod
+        spec.loader.exec_module(mod)
+    return mod
+
+
 def linears():
-    from relax_b200 import synth
-    return synth.LLAMA7B_LINEARS
+    return _synth().LLAMA7B_LINEARS
 
 
 def step_bytes():
-    from relax_b200 import synth
+    synth = _synth()
     return sum(synth.algorithmic_bytes(m, n, k, 4, GROUP) for m in MS for _, k, n in linears())
+
+
+def use_all_host_cores():
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host
+    core.  Must run before liboracle.so (OpenMP) is loaded."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0))
+    except Exception:
+        pass
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    return n
 
 
 def measured_peak():
@@ -62,8 +86,9 @@ def measured_peak():
 def cpu_sample(target_seconds: float):
     """Times the CPU port on a bounded sample of the step: the first `rows` output rows of each
     linear at every M, sized from a probe so that one sample takes about `target_seconds`."""
+    use_all_host_cores()
     from oracle import oracle as orc
-    from relax_b200 import synth
+    synth = _synth()
     C = orc.C()
     g = np.random.Generator(np.random.PCG64(1000))
     cases = {}

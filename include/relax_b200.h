@@ -232,7 +232,9 @@ typedef struct rb200_group_gemm_desc {
   int64_t group_size;     /* <= 0 or >= k: one scale per output channel */
   int64_t scale_stride_n, scale_stride_g, scale_stride_e;
   float zero_const;       /* used when zeros == NULL (FT int4: 8, FT int8: 128, q4f16_1: 7) */
-  int32_t reserved;
+  int32_t indptr_has_prev; /* non-zero: `indptr` points into a longer table and indptr[-1] is the first row of
+                              expert 0 (a rank that holds experts [e0, e1) of a sharded layer passes
+                              table + e0 and w / scales of its own experts; rows outside are left untouched) */
   void* workspace;
   size_t workspace_bytes;
 } rb200_group_gemm_desc;
@@ -324,6 +326,35 @@ RB200_API int rb200_peer_free(void* ptr);
 RB200_API int rb200_peer_export(void* ptr, void* handle_out /* RB200_PEER_HANDLE_BYTES */);
 RB200_API int rb200_peer_import(const void* handle, void** ptr);
 RB200_API int rb200_peer_close(void* ptr);
+
+/*
+ * Row-parallel matmul finished by the sum over ranks, in ONE kernel per rank: the decode-path
+ * (m <= 32) computation of rb200_gemm_fp16_intx on this rank's K-shard, whose epilogue exchanges
+ * the fp32 partial tiles with the peers over NVLink (plain peer stores, flags, plain loads - no
+ * multicast, no collective library), adds them in rank order and only then applies bias /
+ * activation / residual and rounds to fp16.  Every rank ends with the same bits in `out`.
+ * Replaces the pair the reference runs for a row-parallel layer: the matmul followed by
+ * runtime.disco.allreduce (src/runtime/disco/nccl/nccl.cc:90-98) or its customized all-reduce
+ * (src/runtime/disco/cuda_ipc/custom_allreduce.cc:65-105,
+ * 3rdparty/tensorrt_llm/custom_allreduce_kernels.cu:120-169), which sums fp16 partials that were
+ * rounded once already.
+ *   Set-up : every rank allocates rb200_gemm_allreduce_workspace_bytes(max_n) bytes with
+ *            rb200_peer_alloc (zero-filled), exports / imports the handles as for
+ *            rb200_allreduce_oneshot, then a host barrier.  workspaces[p] = this process's address of
+ *            rank p's workspace.
+ *   Calls  : all ranks issue the same sequence of calls (same m, n).  Calls that share a workspace
+ *            must be stream-ordered on each rank.  n <= max_n, m <= 32, k % 64 == 0, symmetric
+ *            weights with per-channel scales or (int4) group-32 [N, K/32] scales; no fused gate/up
+ *            activation, no caller workspace.  Larger batches: rb200_gemm_fp16_intx, then a
+ *            collective library (messages of megabytes are bandwidth-bound, not latency-bound).
+ *   Waits  : bounded (rb200_set_wait_limit_ms); a peer that never arrives leaves `out` unwritten
+ *            for the blocks concerned and sets the status word.
+ * Works under CUDA-graph capture (the call number is kept on the device).  world == 1 is the
+ * plain matmul.
+ */
+RB200_API size_t rb200_gemm_allreduce_workspace_bytes(int64_t max_n);
+RB200_API int rb200_gemm_fp16_intx_allreduce(const rb200_gemm_desc* desc, void* const* workspaces, int rank, int world,
+                                             int64_t max_n, void* stream);
 
 /*
  * Debug/verification entry: writes the dequantised weight wq fp16 [n, k] (row-major) that the

@@ -119,8 +119,10 @@ RB200_API int RB200FuncListGlobalNames(int* out_size, const char*** out_array);
  *       rows), workspace u8 [..]|null, out f16 [M, N])
  *      name and argument list of src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64.
  *  "cutlass.moe_gemm"(x, w_pre i8 [E, K, N/2] | [E, K, N], scales f16 [E, K/g, N] | [E, N],
- *       zeros|null, indptr i64 [E], workspace|null, out)
+ *       zeros|null, indptr i64 [E], workspace|null, out[, indptr_has_prev:int])
  *      the same grouping over FT-layout quantised experts (no counterpart in the reference).
+ *      indptr_has_prev = 1: indptr is a view into a longer table whose element before the view is
+ *      the first row of expert 0 - how a rank that holds experts [e0, e1) of a sharded layer calls.
  *  "relax_b200.moe_gemm_q4f16"(x, w_pre [E, N, K/8] words, scales f16 [E, N, K/g], zeros|null,
  *       indptr i64 [E], group_size:int, zero_const:float, out)
  *  "runtime.get_cuda_stream"() -> handle          src/runtime/cuda/cuda_device_api.cc:318-320

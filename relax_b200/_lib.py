@@ -43,7 +43,7 @@ class GroupGemmDesc(ctypes.Structure):
         ("num_experts", ctypes.c_int64), ("group_size", ctypes.c_int64),
         ("scale_stride_n", ctypes.c_int64), ("scale_stride_g", ctypes.c_int64),
         ("scale_stride_e", ctypes.c_int64),
-        ("zero_const", ctypes.c_float), ("reserved", ctypes.c_int32),
+        ("zero_const", ctypes.c_float), ("indptr_has_prev", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
     ]
 
@@ -96,6 +96,8 @@ SIGNATURES = {
     "rb200_unpack_zeros_autogptq": (_I, [_V, _V, _I64, _I64, _V]),
     "rb200_gemm_fp16_intx": (_I, [ctypes.POINTER(GemmDesc), _V]),
     "rb200_gemm_fp16_intx_noalloc": (_I, [ctypes.POINTER(GemmDesc), _V]),
+    "rb200_gemm_allreduce_workspace_bytes": (ctypes.c_size_t, [_I64]),
+    "rb200_gemm_fp16_intx_allreduce": (_I, [ctypes.POINTER(GemmDesc), ctypes.POINTER(_V), _I, _I, _I64, _V]),
     "rb200_gemm_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64, _I]),
     "rb200_gemm_fp16_int_bias_act": (_I, [_V, _V, _V, _V, _V, _S, _I, _I, _I, _I, _I, _I, _V,
                                           ctypes.c_size_t, _V]),

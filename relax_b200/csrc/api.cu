@@ -318,7 +318,8 @@ size_t rb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int weight_bi
   return plan.partial_bytes + ((plan.counter_ints * sizeof(int) + 255) / 256) * 256 + 256;
 }
 
-int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
+// rb200_gemm_fp16_intx and its row-parallel form share one body; `ar` is nullptr for the former.
+static int gemm_impl(const rb200_gemm_desc* d, const sk::ArCtx* ar, void* stream_v) {
   if (validate_common(d) != 0) return -1;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   RB200_CHECK(d->m >= 0, "m must be >= 0");
@@ -328,6 +329,12 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
   const bool swiglu = d->activation == RB200_ACT_SWIGLU;
   const int64_t ldo = d->ldo > 0 ? d->ldo : (swiglu ? d->n / 2 : d->n);
   RB200_CHECK(aligned16(d->x) && ldx % 8 == 0, "x must be 16-byte aligned with ldx %% 8 == 0");
+  RB200_CHECK(d->activation >= RB200_ACT_IDENTITY && d->activation <= RB200_ACT_SWIGLU, "unknown activation code %d",
+              d->activation);
+  RB200_CHECK(d->binary_op >= RB200_BIN_NONE && d->binary_op <= RB200_BIN_MULTIPLY, "unknown binary_op code %d",
+              d->binary_op);
+  RB200_CHECK(d->unary_op >= RB200_UN_IDENTITY && d->unary_op <= RB200_UN_RELU, "unknown unary_op code %d",
+              d->unary_op);
   RB200_CHECK(d->binary_op == RB200_BIN_NONE || d->residual, "binary_op needs a residual tensor");
   if (swiglu) {
     RB200_CHECK(!d->bias && d->binary_op == RB200_BIN_NONE && d->unary_op == RB200_UN_IDENTITY && !d->workspace,
@@ -335,12 +342,6 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     RB200_CHECK(d->n % 32 == 0, "the fused gate/up activation needs n %% 32 == 0");
   }
   RB200_CHECK(d->bias_stride == 0 || d->bias_stride == d->n, "bias_stride must be 0 or n");
-  RB200_CHECK(d->activation >= RB200_ACT_IDENTITY && d->activation <= RB200_ACT_SWIGLU, "unknown activation code %d",
-              d->activation);
-  RB200_CHECK(d->binary_op >= RB200_BIN_NONE && d->binary_op <= RB200_BIN_MULTIPLY, "unknown binary_op code %d",
-              d->binary_op);
-  RB200_CHECK(d->unary_op >= RB200_UN_IDENTITY && d->unary_op <= RB200_UN_RELU, "unknown unary_op code %d",
-              d->unary_op);
 
   Epilogue epi;
   epi.bias = static_cast<const __half*>(d->bias);
@@ -352,6 +353,12 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
   epi.unop = d->unary_op;
   const int group = (d->group_size <= 0 || d->group_size >= d->k) ? 0 : (int)d->group_size;
 
+  if (ar) {
+    RB200_CHECK(d->m <= 32, "the fused all-reduce form covers the decode path (m <= 32); reduce larger batches with "
+                "a collective library after rb200_gemm_fp16_intx (m=%lld)", (long long)d->m);
+    RB200_CHECK(!d->workspace && !swiglu && d->k % 64 == 0,
+                "the fused all-reduce form takes no caller workspace, no gate/up activation, and needs k %% 64 == 0");
+  }
   if (d->m <= 32 && !d->workspace) {
     DeviceScratch* sc = device_scratch(0, 0);
     if (!sc) return -1;
@@ -373,13 +380,14 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     p.k = (int)d->k;
     p.group = group;
     p.zero_const = d->zero_const;
-    // Which decode kernel: measured crossover on B200.  Few 128-row tiles (n <= 4096): the
-    // cluster kernel, whose split-k partials meet in distributed shared memory.  Otherwise the
-    // stream-k kernel (split-k flags live past the ticket area of the scratch block).
-    if (p.n > 4096) {
+    // Which decode kernel: the stream-k kernel whenever x can be fetched as TMA tiles of whole
+    // 64-k blocks (always for int4); the cluster kernel - split-k partials meeting in distributed
+    // shared memory - for the remaining int8 shapes (k a multiple of 32 only).  Measured on B200
+    // with launch overlap: stream-k is ahead at every size, 8.3 against 9.3 us at k = n = 4096.
+    if (p.k % 64 == 0) {
       unsigned* flags = reinterpret_cast<unsigned*>(sc->counters) + kSkFlagOffset;
       return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
-                         kSkFlagCount, stream);
+                         kSkFlagCount, ar, stream);
     }
     return gemv_cluster_run(p, d->weight_bits, zero_mode(d), sc->sm_count, stream);
   }
@@ -425,6 +433,31 @@ int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) {
     return gemv_launch(p, plan, d->weight_bits, zero_mode(d), stream);
   }
   return gemm_tc_launch(d, epi, group, zero_mode(d), ldx, ldo, stream);
+}
+
+int rb200_gemm_fp16_intx(const rb200_gemm_desc* d, void* stream_v) { return gemm_impl(d, nullptr, stream_v); }
+
+size_t rb200_gemm_allreduce_workspace_bytes(int64_t max_n) {
+  if (max_n <= 0) return 0;
+  return sk::ar_workspace_bytes((unsigned)((max_n + 15) / 16));
+}
+
+int rb200_gemm_fp16_intx_allreduce(const rb200_gemm_desc* d, void* const* workspaces, int rank, int world,
+                                   int64_t max_n, void* stream_v) {
+  RB200_CHECK(world >= 1 && world <= sk::kArMaxRanks, "world=%d outside [1, %d]", world, sk::kArMaxRanks);
+  RB200_CHECK(rank >= 0 && rank < world, "rank=%d outside [0, %d)", rank, world);
+  if (world == 1) return gemm_impl(d, nullptr, stream_v);
+  RB200_CHECK(workspaces != nullptr && max_n > 0, "workspaces must be non-NULL and max_n positive");
+  sk::ArCtx ar;
+  memset(&ar, 0, sizeof(ar));
+  for (int i = 0; i < world; ++i) {
+    RB200_CHECK(workspaces[i] != nullptr, "workspace of rank %d is NULL", i);
+    ar.ws[i] = static_cast<uint8_t*>(workspaces[i]);
+  }
+  ar.rank = rank;
+  ar.world = world;
+  ar.max_blocks = (unsigned)((max_n + 15) / 16);
+  return gemm_impl(d, &ar, stream_v);
 }
 
 static int fill_ft_desc(rb200_gemm_desc* d, const void* A, const void* B, const void* scales,
@@ -523,7 +556,8 @@ int rb200_group_gemm(const rb200_group_gemm_desc* d, void* stream_v) {
   const bool int_zero = d->zero_const >= 0.0f && d->zero_const <= 255.0f && d->zero_const == (float)(int)d->zero_const;
   const int zmode = (packed && (d->zeros || !int_zero)) ? kZeroGeneral : kZeroConstInt;
   const int64_t w_expert_bytes = d->n * d->k * d->weight_bits / 8;
-  return umma_group_gemm_run(p, d->weight_bits, zmode, sc->sm_count, d->indptr, (int)d->num_experts, w_expert_bytes,
+  return umma_group_gemm_run(p, d->weight_bits, zmode, sc->sm_count, d->indptr, d->indptr_has_prev ? 1 : 0,
+                             (int)d->num_experts, w_expert_bytes,
                              packed ? d->scale_stride_e : 0, static_cast<cudaStream_t>(stream_v));
 }
 

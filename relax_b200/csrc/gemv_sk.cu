@@ -1,13 +1,15 @@
 // Host side of the stream-k decode kernel: scale staging mode, pipeline depth, grid, launch.
 #include "gemv_sk.cuh"
 
+#include "tensormap.h"
+
 #include <cstdlib>
 #include <cstring>
 
 namespace rb200 {
 
 int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float* partial, size_t partial_bytes,
-                unsigned* flags, size_t flag_count, cudaStream_t stream) {
+                unsigned* flags, size_t flag_count, const sk::ArCtx* ar, cudaStream_t stream) {
   using namespace sk;
   const int frag = bits == 4 ? 64 : 32;
   const int chunk = frag * kBlocksPerChunk;
@@ -49,18 +51,19 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   p.total_iters = (long long)cpt * n_tiles;
 
   const int ctas_per_sm = 2;
-  const int xpitch = chunk * 2 + (bits == 4 ? 16 : 64);
-  size_t sb = (size_t)kConsumerWarps * kBlocksPerChunk * kTileBytes + (size_t)((l.mt * 8 * xpitch + 127) / 128) * 128;
+  const int x_blocks = chunk / 64;
+  size_t sb = (size_t)kConsumerWarps * kBlocksPerChunk * kTileBytes + (size_t)x_blocks * l.mt * 8 * 128;
   if (l.src != kSrcGlobal) sb += kScaleBoxBytes * (zmode == kZeroGeneral ? 2 : 1);
   const size_t budget = (size_t)(228 * 1024) / ctas_per_sm - 1024;
-  int stages = (int)((budget - 512) / sb);
-  if (stages > 12) stages = 12;
+  int stages = (int)((budget - 1024 - 512) / sb);
+  if (stages > sk::kConsumerWarps) stages = sk::kConsumerWarps;  // one consumer warp starts each stage
   if (stages < 2) stages = 2;
   p.stages = stages;
-  l.smem_bytes = (size_t)stages * sb + (size_t)stages * 2 * sizeof(uint64_t);
+  l.smem_bytes = 1024 + (size_t)stages * sb + (size_t)stages * 2 * sizeof(uint64_t);  // 1 KB: alignment slack
   long long grid = (long long)sm_count * ctas_per_sm;
   if (grid > p.total_iters) grid = p.total_iters;
   l.grid = (int)grid;
+  RB200_CHECK(p.total_iters * grid < (1ll << 31), "problem too large for the decode kernel's 32-bit work split");
 
   const size_t need = (size_t)l.grid * 2 * kConsumerWarps * l.mt * 128 * sizeof(float);
   RB200_CHECK(partial_bytes >= need && flag_count >= (size_t)l.grid * kConsumerWarps,
@@ -68,8 +71,49 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   pp.partial = partial;
   pp.flags = flags;
   pp.wait_limit_ms = wait_limit_ms();
-  if (bits == 4) return launch_sk_i4(pp, l, stream);
-  return launch_sk_i8(pp, l, stream);
+  if (ar && ar->world > 1) {
+    RB200_CHECK(ar->world <= kArMaxRanks && ar->rank >= 0 && ar->rank < ar->world, "bad all-reduce rank %d / world %d",
+                ar->rank, ar->world);
+    RB200_CHECK((unsigned)(p.n / 16) <= ar->max_blocks, "n=%d exceeds the all-reduce workspace (room for n <= %u)", p.n,
+                ar->max_blocks * 16);
+    RB200_CHECK(p.epi.act != kActSwiglu, "the fused gate/up activation cannot be combined with the all-reduce epilogue");
+    pp.ar = *ar;
+  }
+
+  // tensor maps: x as [64-k block][row][64 k] (rows past m and blocks past k read as zero), the
+  // scale / zero tensors as 2-D tiles when they are staged
+  RB200_CHECK(p.k % 64 == 0, "the stream-k decode kernel needs k %% 64 == 0 (k=%d)", p.k);
+  CUtensorMap tx, ts, tz;
+  {
+    const unsigned long long dims[3] = {64ull, (unsigned long long)p.m, (unsigned long long)(p.k / 64)};
+    const unsigned long long strides[2] = {(unsigned long long)p.ldx * 2ull, 128ull};
+    const unsigned box[3] = {64u, (unsigned)(l.mt * 8), (unsigned)x_blocks};
+    if (make_tensor_map(&tx, p.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+      return -1;
+  }
+  ts = tx;
+  tz = tx;
+  pp.s_box_bytes = 0;
+  if (l.src == kSrcSmemNK) {
+    if (make_tensor_map_2d(&ts, p.s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, kg, p.n, kg * 2, 8, kTileRows,
+                           CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
+      return -1;
+    pp.s_box_bytes = 8 * kTileRows * 2;
+    if (pp.has_z_tile && make_tensor_map_2d(&tz, p.z, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, kg, p.n, kg * 2, 8, kTileRows,
+                                            CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
+      return -1;
+  } else if (l.src == kSrcSmemKN) {
+    const unsigned gpc = (unsigned)(chunk / p.group);
+    if (make_tensor_map_2d(&ts, p.s, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.n, kg, (unsigned long long)p.n * 2, kTileRows,
+                           gpc, CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
+      return -1;
+    pp.s_box_bytes = gpc * kTileRows * 2;
+    if (pp.has_z_tile && make_tensor_map_2d(&tz, p.z, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.n, kg,
+                                            (unsigned long long)p.n * 2, kTileRows, gpc, CU_TENSOR_MAP_SWIZZLE_NONE) != 0)
+      return -1;
+  }
+  if (bits == 4) return launch_sk_i4(pp, l, tx, ts, tz, stream);
+  return launch_sk_i8(pp, l, tx, ts, tz, stream);
 }
 
 }  // namespace rb200

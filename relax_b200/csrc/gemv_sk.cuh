@@ -2,27 +2,29 @@
 //
 // What measurements on B200 settled before this version was written:
 //  * mma.sync.m16n8k16 sustains one MMA per 8 clocks per SM sub-partition - a 16x16 weight
-//    fragment (128 packed bytes) per 2 clocks per SM, far above the HBM rate - while tcgen05.mma
-//    pays off only from a batch of a hundred rows up.  Small batches belong on the warp MMA.
-//  * the async copy engine is paid per contiguous segment (about 170 clocks each when one thread
-//    issues them), not per byte.  Hence the stage-contiguous fragment layout (one 16 KB bulk copy
-//    per stage) and 16-byte cp.async for x and the scale tiles.
-//  * the kernel is bound by instruction issue, not by bytes: every warp that polls a barrier
-//    takes issue slots from the eight warps doing the arithmetic.  So one feeder warp (not two)
-//    serves the ring, it sleeps between polls, and the consumers' inner loop carries no test
-//    that can be decided outside it (ragged last chunk, inactive row block).
+//    fragment (128 packed bytes) per 2 clocks per SM, far above the HBM rate - while one
+//    tcgen05.mma (M = 128, K = 16) occupies the tensor pipe for 108 clocks whatever its N up to
+//    192: with the batch as N it caps the weight stream near 2.8 TB/s.  Small batches belong on
+//    the warp MMA; tcgen05 pays off from a batch of a hundred rows up.
+//  * the async copy engine is paid per contiguous segment, not per byte.  Hence the
+//    stage-contiguous fragment layout: one 16 KB bulk copy per stage.
+//  * a warp that issues a 16-byte cp.async stalls until the address is translated - more than a
+//    microsecond at every kernel start, when the weight and scale pages are cold.  Everything a
+//    stage needs therefore travels as bulk / TMA copies, which never stall their issuer.
+//  * registers are handed out per SM sub-partition: a ninth warp (a dedicated producer) costs
+//    every thread 32 of its 128 registers, and a polling producer takes issue slots from the
+//    arithmetic.  There is no producer warp: a ring-full of stages is requested at start-up by
+//    the first lanes of as many warps, and afterwards the warp that finishes a stage last
+//    requests its next fill.
+//  * the only divisions are in the work split, once per warp, 32-bit: 64-bit divisions in a
+//    per-piece helper cost microseconds at every kernel start.
 //  * global fix-up through fences and tickets costs 6-8 us per launch.  Here a CTA does the
 //    pieces of tiles it shares with neighbours first (the tail piece goes to a global slot + a
 //    flag right away, the head piece stays in registers), then its whole tiles, and only at the
 //    very end adds the neighbours' slots - written long before - to its head piece.
 //
-//   feeder warp   : per (128-row tile, k-chunk) stage one bulk async copy of the packed weights
-//                   (lane 0), the scale / zero tiles and the x slice by 16-byte cp.async (all
-//                   lanes), everything counted on the stage's mbarrier.  Weights and scales of
-//                   the first ring-full of stages are requested before the kernel waits for its
-//                   predecessor on the stream; x only after.
-//   8 consumers   : one 16-row block each; 128-bit fragment words from shared memory, bit-exact
-//                   decode in registers, m16n8k16 MMAs into fp32 fragments
+//   8 warps, each one 16-row block of the CTA's 128-row tile; per stage: 128-bit fragment words
+//   from shared memory, bit-exact decode in registers, m16n8k16 MMAs into fp32 fragments
 //
 // Split-k flags are plain 0 / 1 words: the writer of a tail piece sets its flag after the
 // partial sums, the one owner that consumes the piece clears it again, so a launch leaves the
@@ -33,6 +35,8 @@
 // schedules (python/tvm/dlight/gpu/gemv.py:216-530, low_batch_gemv.py:300-613).
 #pragma once
 
+#include <cuda.h>
+
 #include <type_traits>
 
 #include "dequant.cuh"
@@ -42,7 +46,7 @@ namespace rb200 {
 namespace sk {
 
 constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + feeder
+constexpr int kThreads = kConsumerWarps * 32;  // no producer warp: whoever empties a stage refills it
 constexpr int kTileRows = kConsumerWarps * 16;
 constexpr int kBlocksPerChunk = 4;
 constexpr int kTileBytes = 512;
@@ -54,13 +58,15 @@ template <int BITS>
 struct Geo {
   static constexpr int kFrag = BITS == 4 ? 64 : 32;
   static constexpr int kChunk = kFrag * kBlocksPerChunk;                 // 256 / 128 k per stage
-  static constexpr int kXPitch = kChunk * 2 + (BITS == 4 ? 16 : 64);     // bank-conflict free
+  static constexpr int kXBlocks = kChunk / 64;                           // 64-k (128-byte) x blocks per stage
   static constexpr int kWBytes = kConsumerWarps * kBlocksPerChunk * kTileBytes;
 };
 
 template <int BITS, int MT, int ZMODE, int SRC>
 struct StageLayout {
-  static constexpr int kXBytes = ((MT * 8 * Geo<BITS>::kXPitch + 127) / 128) * 128;
+  // x tile of a stage: [64-k block][batch row][128 bytes], 128-byte swizzled by the TMA load
+  static constexpr int kXBlockBytes = MT * 8 * 128;
+  static constexpr int kXBytes = Geo<BITS>::kXBlocks * kXBlockBytes;
   static constexpr int kSOff = Geo<BITS>::kWBytes + kXBytes;
   static constexpr int kSBytes = SRC == kSrcGlobal ? 0 : kScaleBoxBytes;
   static constexpr int kZOff = kSOff + kSBytes;
@@ -68,22 +74,59 @@ struct StageLayout {
   static constexpr int kBytes = kZOff + kZBytes;
 };
 
+// Row-parallel epilogue fused with the sum over ranks (world > 1).  Every rank owns a workspace
+// its peers can address:
+//   [ header 256 B: u32 calls, u32 warps_done | flags u32 [kArMaxRanks][max_blocks] |
+//     data fp32 [2 regions][kArMaxRanks][max_blocks][kArSlotFloats] ]
+// A warp that has the final fp32 fragment of a 16-row block writes it into slot [rank][block] of
+// EVERY rank's workspace (its own included), fences, and stores the call number into flag
+// [rank][block] of every peer.  At the very end of the kernel the same warp waits - bounded -
+// until its own flags [p][block] show the call number for every peer p, adds the slots in rank
+// order (so every rank forms the same bits), applies the epilogue, rounds once and stores.
+// The call number is kept on the device (header), which makes the launch graph-replayable; the
+// two data regions alternate with its parity, because a peer may still be reading call i when
+// this rank is already publishing call i + 1 (it cannot reach call i + 2: that needs the peer's
+// flags of call i + 1, which the peer writes after it finished call i).
+constexpr int kArMaxRanks = 8;
+constexpr int kArSlotFloats = 4 * 128;  // four m-tiles of one 16-row block
+constexpr size_t kArHeaderBytes = 256;
+struct ArCtx {
+  uint8_t* ws[kArMaxRanks];  // ws[r]: rank r's workspace as this GPU addresses it
+  int rank, world;           // world <= 1: no exchange
+  unsigned max_blocks;       // 16-row blocks a region has room for
+};
+__host__ __device__ __forceinline__ size_t ar_flags_bytes(unsigned max_blocks) {
+  return (((size_t)kArMaxRanks * max_blocks * 4) + 255) / 256 * 256;
+}
+__host__ __device__ __forceinline__ size_t ar_workspace_bytes(unsigned max_blocks) {
+  return kArHeaderBytes + ar_flags_bytes(max_blocks) + (size_t)2 * kArMaxRanks * max_blocks * kArSlotFloats * 4;
+}
+
 struct Params {
   GemvParams g;
+  ArCtx ar;
   float* partial;     // [grid][2][8 warps][MT][4][32] fp32: slot 0 tail piece (for the owner), slot 1 own head piece
   unsigned* flags;    // [grid][8]: 1 while a tail piece waits for its owner, 0 at rest
   int has_z_tile;
+  unsigned s_box_bytes;    // bytes one scale (or zero) TMA tile delivers
   unsigned wait_limit_ms;  // bound of the fix-up wait (0: about two seconds)
 };
 
 #ifdef __CUDACC__
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes)
-               : "memory");
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
 }
-__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      : "memory");
 }
 __device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -93,57 +136,69 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ long long range_start(long long cta, long long total, long long grid) {
-  return cta * total / grid;
-}
-
 enum PieceKind : int { kWhole = 0, kTail = 1, kHead = 2 };
 struct Piece {
   int tile, c0, c1, kind;
 };
-// Pieces of a CTA's contiguous iteration range in execution order: the tail piece (a tile begun
-// by an earlier CTA), the head piece (a tile this CTA begins and others finish), whole tiles.
-__device__ __forceinline__ bool get_piece(long long it0, long long it1, int cpt, int idx, Piece& pc) {
-  if (it0 >= it1) return false;
-  const int first_tile = (int)(it0 / cpt), last_tile = (int)((it1 - 1) / cpt);
-  const int fc0 = (int)(it0 % cpt);
-  const int lc1 = (int)((it1 - 1) % cpt) + 1;
-  const bool has_tail = fc0 != 0;
-  const bool single = first_tile == last_tile;
-  const bool has_head = lc1 != cpt && !(single && has_tail);
-  int n = 0;
-  if (has_tail) {
-    if (idx == n) {
-      pc.tile = first_tile;
-      pc.c0 = fc0;
-      pc.c1 = single ? lc1 : cpt;
-      pc.kind = kTail;
-      return true;
-    }
-    ++n;
+// A CTA's contiguous range [it0, it1) of (tile, chunk) iterations, cut into pieces in execution
+// order: the tail piece (a tile begun by an earlier CTA), the head piece (a tile this CTA begins
+// and others finish), then whole tiles.  Built once per warp (the only divisions of the kernel,
+// 32-bit); piece(idx) afterwards is compares and adds.
+struct PiecePlan {
+  int first_tile, last_tile, fc0, lc1, cpt;
+  int w0, w1;  // whole tiles w0 .. w1 inclusive
+  bool has_tail, has_head, single, any;
+
+  __device__ __forceinline__ void build(unsigned cta, unsigned total, unsigned grid, int cpt_) {
+    const unsigned it0 = cta * total / grid;  // total * grid < 2^31 (checked by the host)
+    const unsigned it1 = (cta + 1) * total / grid;
+    cpt = cpt_;
+    any = it0 < it1;
+    first_tile = (int)(it0 / (unsigned)cpt_);
+    fc0 = (int)(it0 - (unsigned)first_tile * (unsigned)cpt_);
+    const unsigned l = any ? it1 - 1 : it0;
+    last_tile = (int)(l / (unsigned)cpt_);
+    lc1 = (int)(l - (unsigned)last_tile * (unsigned)cpt_) + 1;
+    has_tail = fc0 != 0;
+    single = first_tile == last_tile;
+    has_head = lc1 != cpt_ && !(single && has_tail);
+    w0 = first_tile + (has_tail ? 1 : 0);
+    w1 = last_tile - ((has_head || (single && has_tail)) ? 1 : 0);
   }
-  if (has_head) {
-    if (idx == n) {
-      pc.tile = last_tile;
+  __device__ __forceinline__ bool piece(int idx, Piece& pc) const {
+    if (!any) return false;
+    int n = 0;
+    if (has_tail) {
+      if (idx == 0) {
+        pc.tile = first_tile;
+        pc.c0 = fc0;
+        pc.c1 = single ? lc1 : cpt;
+        pc.kind = kTail;
+        return true;
+      }
+      n = 1;
+    }
+    if (has_head) {
+      if (idx == n) {
+        pc.tile = last_tile;
+        pc.c0 = 0;
+        pc.c1 = lc1;
+        pc.kind = kHead;
+        return true;
+      }
+      ++n;
+    }
+    const int t = w0 + idx - n;
+    if (t <= w1) {
+      pc.tile = t;
       pc.c0 = 0;
-      pc.c1 = lc1;
-      pc.kind = kHead;
+      pc.c1 = cpt;
+      pc.kind = kWhole;
       return true;
     }
-    ++n;
+    return false;
   }
-  const int w0 = first_tile + (has_tail ? 1 : 0);
-  const int w1 = last_tile - ((has_head || (single && has_tail)) ? 1 : 0);  // inclusive
-  const int wi = idx - n;
-  if (w0 + wi <= w1) {
-    pc.tile = w0 + wi;
-    pc.c0 = 0;
-    pc.c1 = cpt;
-    pc.kind = kWhole;
-    return true;
-  }
-  return false;
-}
+};
 
 template <int BITS, int GROUP>
 struct ScalePlan {
@@ -154,26 +209,41 @@ struct ScalePlan {
   static constexpr int kCount = kChunk / kSpan;
 };
 
-// Feeder-side wait: a failed poll is followed by a sleep, so a feeder that is ahead of the
-// consumers costs them next to no issue slots.  Bounded like every other wait.
-__device__ __forceinline__ bool mbar_wait_sleepy(uint64_t* bar, uint32_t parity, int* status) {
-#pragma unroll 1
-  for (int i = 0; i < (1 << 23); ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(200);
-  }
-  if (status) atomicExch(status, kStatusWaitTimeout);
-  return false;
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_volatile_f32(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned atom_inc_acq_rel_shared(unsigned* p) {
+  unsigned old;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(p)) : "memory");
+  return old;
 }
 
-template <int BITS, int MT, int ZMODE, int GROUP, int SRC>
-__global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
+// AR: compiled with the all-reduce epilogue (a separate instantiation, so that the plain kernel
+// carries none of its code or registers).
+template <int BITS, int MT, int ZMODE, int GROUP, int SRC, bool AR = false>
+__global__ void __launch_bounds__(kThreads, 2)
+    gemv_sk_kernel(const Params pp, const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_s,
+                   const __grid_constant__ CUtensorMap tmap_z) {
   using G = Geo<BITS>;
   using L = StageLayout<BITS, MT, ZMODE, SRC>;
   using SP = ScalePlan<BITS, GROUP>;
   constexpr int kStage = L::kBytes;
-  constexpr int kChains = MT <= 2 ? 2 : 1;  // independent MMA chains per m-tile
-  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kChains = MT <= 2 ? 2 : 1;  // independent MMA chains per m-tile (four m-tiles are four already)
+  extern __shared__ uint8_t smem_raw[];
+  // stages start on 1 KB boundaries: the x tile's 128-byte swizzle is a function of the address
+  // (an offset from the array, not a pointer rebuilt from an integer: the compiler must keep
+  // seeing shared memory, or every fragment read turns into a generic load)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const GemvParams& p = pp.g;
 
   const int stages = p.stages;
@@ -181,17 +251,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   const int warp = tid >> 5;
   const int lane = tid & 31;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStage);
-  uint64_t* empty_bar = full_bar + stages;
+  unsigned* drained = reinterpret_cast<unsigned*>(full_bar + stages);  // per stage: warps done with its current fill
 
-  // x rows >= m are never written by the feeder and must read as zero
-  for (int s = 0; s < stages; ++s) {
-    uint32_t* xs = reinterpret_cast<uint32_t*>(smem + (size_t)s * kStage + G::kWBytes);
-    for (int i = tid; i < L::kXBytes / 4; i += kThreads) xs[i] = 0u;
-  }
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1 + 32);  // lane 0's expect_tx arrival + 32 lanes of cp.async
-      mbar_init(&empty_bar[s], kConsumerWarps);
+      mbar_init(&full_bar[s], 1);  // the issuing lane's expect_tx arrival; the copies complete the bytes
+      drained[s] = 0u;
     }
     mbar_fence_init();
   }
@@ -200,117 +265,64 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   griddep_launch_dependents();
 
   const int cta = blockIdx.x;
-  const long long total = p.total_iters;
-  const long long grid = gridDim.x;
-  const long long it0 = range_start(cta, total, grid);
-  const long long it1 = range_start(cta + 1, total, grid);
+  const unsigned total = (unsigned)p.total_iters;  // the host checks that total * grid fits 32 bits
+  const unsigned grid = gridDim.x;
   const int cpt = p.chunks_per_tile;
+  PiecePlan plan;
+  plan.build((unsigned)cta, total, grid, cpt);
   const int kb_total = p.k / G::kFrag;
   const int n_blocks = p.n / 16;
 
-  if (warp == kConsumerWarps) {
-    // ------------------------------------------------------------ feeder
-    const int64_t kg = GROUP > 0 ? p.k / GROUP : 0;
-    constexpr int kXChunks = G::kChunk * 2 / 16;  // 16-byte pieces per x row per stage (32 / 16)
-
-    auto feed_w = [&](int tile, int chunk, int stage) {  // packed weights + scale / zero tiles
-      uint8_t* sbase = smem + (size_t)stage * kStage;
-      if (lane == 0) {
-        const int nblk = min(kConsumerWarps, n_blocks - tile * kConsumerWarps);
-        const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
-        const uint32_t wbytes = (uint32_t)(nkb * nblk) * kTileBytes;  // contiguous in the fragment layout
-        mbar_arrive_expect_tx(&full_bar[stage], wbytes);
-        bulk_g2s(sbase, p.w + frag_stage_offset(tile, chunk, n_blocks, kb_total), wbytes, &full_bar[stage]);
+  // ---------------------------------------------------------------- filling one stage
+  // Everything a stage needs travels on the async copy engine and is counted in bytes on the
+  // stage's barrier; the issuing lane never waits on a load (16-byte cp.async copies did: their
+  // issue stalled for a microsecond and more at every kernel start).
+  //   weights : one bulk copy, contiguous in the fragment layout
+  //   scales / zero points : one TMA tile each (when their layout is one of the regular forms)
+  //   x : one TMA tile [64-k blocks][MT*8 rows][128 B], 128-byte swizzle (conflict-free fragment
+  //       reads); rows past m and k past the end read as zero
+  constexpr uint32_t kXTx = (uint32_t)L::kXBytes;
+  auto feed_w = [&](int tile, int chunk, int stage) {  // one lane: weights + scale / zero tiles
+    uint8_t* sb = smem + (size_t)stage * kStage;
+    const int nblk = min(kConsumerWarps, n_blocks - tile * kConsumerWarps);
+    const int nkb = min(kBlocksPerChunk, kb_total - chunk * kBlocksPerChunk);
+    const uint32_t wbytes = (uint32_t)(nkb * nblk) * kTileBytes;
+    uint32_t tx = wbytes + kXTx;
+    if (SRC != kSrcGlobal) tx += pp.s_box_bytes * ((ZMODE == kZeroGeneral && pp.has_z_tile) ? 2u : 1u);
+    mbar_arrive_expect_tx(&full_bar[stage], tx);
+    bulk_g2s(sb, p.w + frag_stage_offset(tile, chunk, n_blocks, kb_total), wbytes, &full_bar[stage]);
+    if (SRC != kSrcGlobal) {
+      // coordinates: NK tensor {group, row}; KN tensor {row, group}
+      constexpr int kGroupsPerChunk = GROUP > 0 ? (G::kChunk / GROUP) : 1;
+      const int gc0 = chunk * kGroupsPerChunk, r0 = tile * kTileRows;
+      if (SRC == kSrcSmemNK) tma_load_2d(sb + L::kSOff, &tmap_s, gc0, r0, &full_bar[stage]);
+      else tma_load_2d(sb + L::kSOff, &tmap_s, r0, gc0, &full_bar[stage]);
+      if (ZMODE == kZeroGeneral && pp.has_z_tile) {
+        if (SRC == kSrcSmemNK) tma_load_2d(sb + L::kZOff, &tmap_z, gc0, r0, &full_bar[stage]);
+        else tma_load_2d(sb + L::kZOff, &tmap_z, r0, gc0, &full_bar[stage]);
       }
-      const int64_t n0 = (int64_t)tile * kTileRows;
-      if (SRC == kSrcSmemNK) {
-        // [128 rows][8 groups]: 16 bytes per row
-        const int64_t g0 = (int64_t)chunk * 8;
-        const int64_t left = (kg - g0) * 2;
-        const uint32_t sv = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = lane + 32 * i;
-          const bool in = n0 + row < p.n;
-          const int64_t o = (in ? (n0 + row) : 0) * kg + (sv ? g0 : 0);
-          cp_async16(sbase + L::kSOff + row * 16, p.s + o, in ? sv : 0u);
-          if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + L::kZOff + row * 16, p.z + o, in ? sv : 0u);
-        }
-      } else if (SRC == kSrcSmemKN) {
-        // [groups of the chunk][128 rows]: 256 bytes per group row
-        constexpr int kG = GROUP > 0 ? (G::kChunk / GROUP) : 1;
-        for (int i = lane; i < kG * 16; i += 32) {
-          const int gl = i >> 4, cc = i & 15;
-          const int64_t grow = (int64_t)chunk * kG + gl;
-          const bool in = grow < kg && n0 + cc * 8 < p.n;
-          const int64_t o = (in ? grow : 0) * p.n + (in ? n0 + cc * 8 : 0);
-          cp_async16(sbase + L::kSOff + gl * 256 + cc * 16, p.s + o, in ? 16u : 0u);
-          if (ZMODE == kZeroGeneral && pp.has_z_tile) cp_async16(sbase + L::kZOff + gl * 256 + cc * 16, p.z + o, in ? 16u : 0u);
-        }
-      }
-    };
-    auto feed_x = [&](int chunk, int stage) {  // x[r, chunk*kChunk + c*8 .. +8) -> row r of the stage's x tile
-      uint8_t* sbase = smem + (size_t)stage * kStage;
-      for (int i = lane; i < p.m * kXChunks; i += 32) {
-        const int r = i / kXChunks, c = i % kXChunks;
-        const int64_t kcol = (int64_t)chunk * G::kChunk + c * 8;
-        const uint32_t v = kcol < p.k ? 16u : 0u;
-        cp_async16(sbase + G::kWBytes + r * G::kXPitch + c * 16, p.x + (int64_t)r * p.ldx + (v ? kcol : 0), v);
-      }
-      cp_async_arrive(&full_bar[stage]);
-    };
-
-    // The first ring-full of stages needs no wait (every stage starts empty): request their
-    // weights and scales at once, then wait for the previous kernel on the stream - activations
-    // may be its output - and only then fetch x for them.
+    }
+  };
+  auto feed_x = [&](int chunk, int stage) {  // one lane: the x tile of the stage
+    tma_load_3d(smem + (size_t)stage * kStage + G::kWBytes, &tmap_x, 0, 0, chunk * G::kXBlocks, &full_bar[stage]);
+  };
+  // Walker over this CTA's (tile, chunk) stages in execution order.
+  struct Walker {
     Piece pc;
-    int idx = 0, chunk = 0;
-    bool have = get_piece(it0, it1, cpt, 0, pc);
-    if (have) chunk = pc.c0;
-    auto advance = [&]() {
-      if (++chunk >= pc.c1) {
-        have = get_piece(it0, it1, cpt, ++idx, pc);
-        if (have) chunk = pc.c0;
-      }
-    };
-    {
-      Piece pc0 = pc;
-      const int idx0 = idx, chunk0 = chunk;
-      const bool have0 = have;
-      int primed = 0;
-      for (; have && primed < stages; ++primed) {
-        feed_w(pc.tile, chunk, primed);
-        advance();
-      }
-      griddep_wait();
-      pc = pc0;
-      idx = idx0;
-      chunk = chunk0;
-      have = have0;
-      for (int s = 0; s < primed; ++s) {
-        feed_x(chunk, s);
-        advance();
-      }
+    int idx, chunk;
+    bool have;
+  };
+  auto w_begin = [&](Walker& w) {
+    w.idx = 0;
+    w.have = plan.piece(0, w.pc);
+    w.chunk = w.have ? w.pc.c0 : 0;
+  };
+  auto w_next = [&](Walker& w) {
+    if (++w.chunk >= w.pc.c1) {
+      w.have = plan.piece(++w.idx, w.pc);
+      if (w.have) w.chunk = w.pc.c0;
     }
-    int stage = 0;        // after a full ring the next stage to fill is 0 again (primed == stages),
-    uint32_t phase = 1;   // now on its second use; with fewer iterations than stages nothing is left
-    bool ok = true;
-    while (ok && have) {
-      if (!mbar_wait_sleepy(&empty_bar[stage], phase ^ 1u, p.status)) {
-        ok = false;
-        break;
-      }
-      feed_w(pc.tile, chunk, stage);
-      feed_x(chunk, stage);
-      advance();
-      if (++stage == stages) {
-        stage = 0;
-        phase ^= 1u;
-      }
-    }
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    return;
-  }
+  };
 
   // -------------------------------------------------------------- consumer warps
   const int g = lane >> 2;
@@ -321,6 +333,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   const int lane_k = t * (G::kFrag / 4);
   const uint32_t half_sel = (t >> 1) ? 0x3232u : 0x1010u;
   const int unit = frag_unit_pos(lane);
+  // byte offset of this lane's x pieces inside a 128-byte swizzled row: int4 - pieces 2t and 2t + 1
+  // of the 64-k block; int8 - piece t of the even / odd 32-k fragment tile of the block
+  const int x_off[2] = {BITS == 4 ? ((2 * t) ^ g) << 4 : (t ^ g) << 4, BITS == 4 ? ((2 * t + 1) ^ g) << 4 : ((4 + t) ^ g) << 4};
 
   float acc[MT][kChains][4];
   // the head piece waits for the other CTAs' parts: in registers for one or two m-tiles, in this
@@ -328,9 +343,33 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
   constexpr bool kHeadInRegs = MT <= 2;
   float head[kHeadInRegs ? MT : 1][4];
   bool have_head = false;
+  bool head_published = false;
   int head_tile = 0;
   uint32_t s_cur[SP::kCount], s_nxt[SP::kCount];
   uint32_t z_cur[SP::kCount], z_nxt[SP::kCount];
+
+  // Start-up: lane 0 of consumer warp w requests the first fill of stage w - a ring-full of
+  // copies leaves within one warp's instruction latency instead of queueing behind one another.
+  // Weights and scales do not depend on the previous kernel on the stream and go out at once;
+  // x follows after the dependency wait.
+  if (warp < stages) {
+    Walker w;
+    w_begin(w);
+    for (int i = 0; i < warp && w.have; ++i) w_next(w);
+    if (w.have) {
+      if (lane == 0) feed_w(w.pc.tile, w.chunk, warp);
+      griddep_wait();
+      if (lane == 0) feed_x(w.chunk, warp);
+      __syncwarp();
+    }
+  }
+
+  // `ahead` names the iteration that will next be loaded into the stage being consumed: one
+  // ring-length past the consumer.  Every warp tracks it; the warp that finishes a stage last
+  // (shared-memory counter) issues that load.
+  Walker ahead;
+  w_begin(ahead);
+  for (int i = 0; i < stages && ahead.have; ++i) w_next(ahead);
 
   int stage = 0;
   uint32_t phase = 0;
@@ -364,7 +403,72 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
       }
   };
 
-  for (int idx = 0; ok && get_piece(it0, it1, cpt, idx, pc); ++idx) {
+  // ---- all-reduce side of the epilogue (see ArCtx)
+  const bool ar_on = AR && pp.ar.world > 1;
+  unsigned ar_call = 0;
+  auto ar_slot = [&](int r, unsigned call, int src, int blk) -> float* {
+    return reinterpret_cast<float*>(pp.ar.ws[r] + kArHeaderBytes + ar_flags_bytes(pp.ar.max_blocks)) +
+           ((size_t)((call & 1u) * kArMaxRanks + (unsigned)src) * pp.ar.max_blocks + (unsigned)blk) * kArSlotFloats;
+  };
+  auto ar_flag = [&](int r, int src, int blk) -> unsigned* {
+    return reinterpret_cast<unsigned*>(pp.ar.ws[r] + kArHeaderBytes) + (size_t)src * pp.ar.max_blocks + blk;
+  };
+  // this rank's part of a block is final: hand it to every rank
+  auto ar_publish = [&](const float (&v)[MT][4], int tile_i) {
+    const int blk = tile_i * kConsumerWarps + warp;
+    if (blk >= n_blocks) return;
+    for (int r = 0; r < pp.ar.world; ++r) {
+      float* dst = ar_slot(r, ar_call, pp.ar.rank, blk) + lane;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dst[(mt * 4 + c) * 32] = v[mt][c];
+    }
+    __syncwarp();
+    if (lane < pp.ar.world && lane != pp.ar.rank) {
+      __threadfence_system();
+      st_release_sys_u32(ar_flag(lane, pp.ar.rank, blk), ar_call);
+    }
+  };
+  // all ranks' parts of a block: wait, add in rank order, finish
+  auto ar_finish = [&](int tile_i, unsigned long long limit_ns) -> bool {
+    const int blk = tile_i * kConsumerWarps + warp;
+    if (blk >= n_blocks) return true;
+    bool arrived = true;
+    if (lane < pp.ar.world && lane != pp.ar.rank) {
+      const unsigned* f = ar_flag(pp.ar.rank, lane, blk);
+      if ((int)(ld_acquire_sys_u32(f) - ar_call) < 0) {
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        while ((int)(ld_acquire_sys_u32(f) - ar_call) < 0) {  // flags only grow: a peer may be a call ahead
+          unsigned long long t1;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+          if (t1 - t0 > limit_ns) {
+            if (p.status) atomicExch(p.status, kStatusWaitTimeout);
+            arrived = false;
+            break;
+          }
+        }
+      }
+    }
+    if (!__all_sync(0xffffffffu, arrived)) return false;
+    float sum[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sum[mt][c] = 0.0f;
+    for (int r = 0; r < pp.ar.world; ++r) {
+      const float* src = ar_slot(pp.ar.rank, ar_call, r, blk) + lane;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sum[mt][c] += ld_volatile_f32(src + (mt * 4 + c) * 32);
+    }
+    store_tile(sum, tile_i);
+    return true;
+  };
+
+  for (int idx = 0; ok && plan.piece(idx, pc); ++idx) {
     const int blk = pc.tile * kConsumerWarps + warp;
     const bool active = blk < n_blocks;
 #pragma unroll
@@ -396,7 +500,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
     auto consume = [&](auto full, int nkb) {
       constexpr bool kFull = decltype(full)::value;
       const uint4* wsm = reinterpret_cast<const uint4*>(sbase + warp * ((kFull ? kBlocksPerChunk : nkb) * kTileBytes)) + unit;
-      const uint8_t* xsm = sbase + G::kWBytes + g * G::kXPitch + t * (G::kFrag / 2);
+      // this lane's 16-byte pieces of x: row g of every m-tile, swizzled position (piece ^ g)
+      const uint8_t* xsm = sbase + G::kWBytes + g * 128;
       uint4 nk_s_g, nk_s_g8, nk_z_g, nk_z_g8;
       if (SRC == kSrcSmemNK) {
         const uint4* sp = reinterpret_cast<const uint4*>(sbase + L::kSOff) + warp * 16 + g;
@@ -453,7 +558,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
               if ((j & 1) == 0) {
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
-                  xv[mt][j >> 1] = *reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 128 + (j >> 1) * 16);
+                  xv[mt][j >> 1] = *reinterpret_cast<const uint4*>(xsm + kb * L::kXBlockBytes + mt * 1024 + x_off[j >> 1]);
               }
               uint32_t a[4];
               decode_int4_word<ZMODE>(ww[j], zc, s_g, s_g8, z_g, z_g8, a);
@@ -469,7 +574,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
             uint4 xv[MT];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
-              xv[mt] = *reinterpret_cast<const uint4*>(xsm + mt * 8 * G::kXPitch + kb * 64);
+              xv[mt] = *reinterpret_cast<const uint4*>(xsm + (kb >> 1) * L::kXBlockBytes + mt * 1024 + x_off[kb & 1]);
             uint32_t a[4];
             decode_int8_pair<ZMODE>(wv.x, wv.y, zc, s_g, s_g8, z_g, z_g8, a);
 #pragma unroll
@@ -501,7 +606,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
         else consume(std::false_type{}, nkb);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (lane == 0 && atom_inc_acq_rel_shared(&drained[stage]) == kConsumerWarps - 1) {
+        drained[stage] = 0u;  // visible to the other warps through the stage's barrier, like the data
+        if (ahead.have) {
+          feed_w(ahead.pc.tile, ahead.chunk, stage);
+          feed_x(ahead.chunk, stage);
+        }
+      }
+      w_next(ahead);
       sbase += kStage;
       if (++stage == stages) {
         stage = 0;
@@ -525,8 +637,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
 
     // outputs and scratch may still be in use by the previous kernel until it has ended
     griddep_wait();
+    if (ar_on && ar_call == 0) ar_call = *reinterpret_cast<volatile unsigned*>(pp.ar.ws[pp.ar.rank]) + 1u;
     if (pc.kind == kWhole) {
-      store_tile(fin, pc.tile);
+      if (ar_on) ar_publish(fin, pc.tile);
+      else store_tile(fin, pc.tile);
     } else if (pc.kind == kHead) {
       have_head = true;
       head_tile = pc.tile;
@@ -557,25 +671,33 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
 
   // ---------------------------------------------------------------- fix-up of the owned tile
   if (ok && have_head) {
-    const long long hi_it = (long long)head_tile * cpt + cpt - 1;
-    const int last_cta = (int)(((hi_it + 1) * grid - 1) / total);
+    // the last CTA whose range reaches into the owned tile
+    const unsigned hi_it = (unsigned)head_tile * (unsigned)cpt + (unsigned)cpt - 1u;
+    const int last_cta = (int)(((hi_it + 1u) * grid - 1u) / total);
     const unsigned long long limit_ns = (pp.wait_limit_ms ? (unsigned long long)pp.wait_limit_ms : 2000ull) * 1000000ull;
+    // one contributor per lane: all flags are polled at once (polled one after another, every
+    // contributor cost a round trip to L2 even when its flag was long set)
     bool flags_ok = true;
-    for (int c = cta + 1; c <= last_cta && flags_ok; ++c) {
-      const unsigned* f = pp.flags + c * kConsumerWarps + warp;
-      if (ld_acquire_u32(f) != 0u) continue;
-      unsigned long long t0;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-      while (ld_acquire_u32(f) == 0u) {
-        __nanosleep(64);
-        unsigned long long t1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (t1 - t0 > limit_ns) {  // give up, report, leave the tile unwritten
-          if (p.status) atomicExch(p.status, kStatusWaitTimeout);
-          flags_ok = false;
-          break;
+    for (int c0 = cta + 1; c0 <= last_cta && flags_ok; c0 += 32) {
+      const int c = c0 + lane;
+      if (c <= last_cta) {
+        const unsigned* f = pp.flags + c * kConsumerWarps + warp;
+        if (ld_acquire_u32(f) == 0u) {
+          unsigned long long t0;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+          while (ld_acquire_u32(f) == 0u) {
+            __nanosleep(256);
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > limit_ns) {  // give up, report, leave the tile unwritten
+              if (p.status) atomicExch(p.status, kStatusWaitTimeout);
+              flags_ok = false;
+              break;
+            }
+          }
         }
       }
+      flags_ok = __all_sync(0xffffffffu, flags_ok);
     }
     flags_ok = __all_sync(0xffffffffu, flags_ok);
     if (flags_ok) {
@@ -604,7 +726,38 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_sk_kernel(const Params pp) {
       __syncwarp();
       if (lane == 0)
         for (int c = cta + 1; c <= last_cta; ++c) pp.flags[c * kConsumerWarps + warp] = 0u;
-      store_tile(sum, head_tile);
+      if (ar_on) {
+        ar_publish(sum, head_tile);
+        head_published = true;
+      } else {
+        store_tile(sum, head_tile);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- sum over ranks
+  if (ar_on) {
+    const unsigned long long limit_ns = (pp.wait_limit_ms ? (unsigned long long)pp.wait_limit_ms : 2000ull) * 1000000ull;
+    if (ok) {
+      // the blocks this warp published: its whole tiles, then the tile it owns
+      bool fine = true;
+      for (int idx = 0; fine && plan.piece(idx, pc); ++idx)
+        if (pc.kind == kWhole) fine = ar_finish(pc.tile, limit_ns);
+      if (fine && head_published) ar_finish(head_tile, limit_ns);
+    }
+    // the call is over when every warp of the grid is through: the last one advances the
+    // device-side call number (read by the next launch after its dependency wait)
+    griddep_wait();
+    if (ar_call == 0) ar_call = *reinterpret_cast<volatile unsigned*>(pp.ar.ws[pp.ar.rank]) + 1u;
+    __syncwarp();
+    if (lane == 0) {
+      unsigned* hdr = reinterpret_cast<unsigned*>(pp.ar.ws[pp.ar.rank]);
+      __threadfence();
+      if (atomicAdd(hdr + 1, 1u) == grid * kConsumerWarps - 1u) {
+        hdr[1] = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(hdr) = ar_call;
+      }
     }
   }
 }
@@ -616,14 +769,17 @@ struct Launch {
   int grid;
   size_t smem_bytes;
 };
-int launch_sk_i4(const Params& pp, const Launch& l, cudaStream_t stream);
-int launch_sk_i8(const Params& pp, const Launch& l, cudaStream_t stream);
+int launch_sk_i4(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& ts, const CUtensorMap& tz,
+                 cudaStream_t stream);
+int launch_sk_i8(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& ts, const CUtensorMap& tz,
+                 cudaStream_t stream);
 
 }  // namespace sk
 
 // Host entry: plans and launches the stream-k decode kernel.  `partial` / `flags` are scratch;
 // the flags must be zero before the first launch and are left zero by every launch.
+// `ar` (may be nullptr): finish the call with the sum over ranks, see sk::ArCtx.
 int gemv_sk_run(const GemvParams& p, int bits, int zmode, int sm_count, float* partial, size_t partial_bytes,
-                unsigned* flags, size_t flag_count, cudaStream_t stream);
+                unsigned* flags, size_t flag_count, const sk::ArCtx* ar, cudaStream_t stream);
 
 }  // namespace rb200

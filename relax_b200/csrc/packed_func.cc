@@ -586,7 +586,8 @@ int pf_group_gemm_fp16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret
 // [E, K, N] (int8) as written by cutlass.ft_preprocess_weight, scales [E, K/g, N] or [E, N].
 // layout 1 (relax_b200.moe_gemm_q4f16): w_pre [E, N, K/8] 32-bit words, scales [E, N, K/g].
 int moe_gemm(const char* fname, int layout, const DLTensor* x, const DLTensor* w, const DLTensor* s,
-             const DLTensor* z, const DLTensor* indptr, const DLTensor* out, int64_t group, double zero_const) {
+             const DLTensor* z, const DLTensor* indptr, const DLTensor* out, int64_t group, double zero_const,
+             int64_t indptr_has_prev = 0) {
   PF_CHECK(x->ndim == 2 && w->ndim == 3 && indptr->ndim == 1 && out->ndim == 2,
            "%s: expected x 2-D, weight 3-D, indptr 1-D, out 2-D", fname);
   if (check_tensor(fname, "x", x, kDLFloat, 16) || check_tensor(fname, "scales", s, kDLFloat, 16) ||
@@ -636,19 +637,22 @@ int moe_gemm(const char* fname, int layout, const DLTensor* x, const DLTensor* w
   d.n = n;
   d.k = k;
   d.num_experts = E;
+  d.indptr_has_prev = indptr_has_prev ? 1 : 0;
   return rb200_group_gemm(&d, rb200_get_stream());
 }
-// (x, w_pre, scales, zeros|null, indptr, workspace|null, out)
+// (x, w_pre, scales, zeros|null, indptr, workspace|null, out[, indptr_has_prev:int])
 int pf_moe_gemm(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {
   const char* fname = "cutlass.moe_gemm";
   Args a{v, tc, n_args, fname};
-  PF_CHECK(n_args == 7, "%s expects 7 arguments, got %d", fname, n_args);
+  PF_CHECK(n_args == 7 || n_args == 8, "%s expects 7 or 8 arguments, got %d", fname, n_args);
   const DLTensor *x, *w, *s, *z, *indptr, *ws, *out;
+  int64_t has_prev = 0;
   if (a.tensor(0, &x) || a.tensor(1, &w) || a.tensor(2, &s) || a.tensor(3, &z, true) || a.tensor(4, &indptr) ||
       a.tensor(5, &ws, true) || a.tensor(6, &out))
     return -1;
+  if (n_args == 8 && a.integer(7, &has_prev)) return -1;
   if (ret_tc) *ret_tc = RB200_ARG_NULL;
-  return moe_gemm(fname, 0, x, w, s, z, indptr, out, 0, 0.0);
+  return moe_gemm(fname, 0, x, w, s, z, indptr, out, 0, 0.0, has_prev);
 }
 // (x, w_pre, scales, zeros|null, indptr, group_size, zero_const, out)
 int pf_moe_gemm_q4f16(RB200Value* v, int* tc, int n_args, RB200Value*, int* ret_tc, void*) {

@@ -1,5 +1,6 @@
 #include "tensormap.h"
 
+#include <cstring>
 #include <mutex>
 
 namespace rb200 {
@@ -24,11 +25,53 @@ static int resolve_encode() {
   return 0;
 }
 
+namespace {
+// Encoding a tensor map costs a driver call of a microsecond or two; a serving loop asks for the
+// same few maps (same buffers, same shapes) on every step.  Small per-thread cache, keyed by
+// everything the encoding depends on.
+struct MapKey {
+  const void* base;
+  int dtype, rank, swizzle;
+  unsigned long long dims[5], strides[4];
+  unsigned box[5];
+  bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kMapCacheSlots = 256;
+thread_local MapEntry t_map_cache[kMapCacheSlots];
+unsigned hash_key(const MapKey& k) {
+  const unsigned char* b = reinterpret_cast<const unsigned char*>(&k);
+  unsigned h = 2166136261u;
+  for (size_t i = 0; i < sizeof(MapKey); ++i) h = (h ^ b[i]) * 16777619u;
+  return h;
+}
+}  // namespace
+
 int make_tensor_map(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int rank,
                     const unsigned long long* dims, const unsigned long long* strides_bytes,
                     const unsigned* box, CUtensorMapSwizzle swizzle) {
-  if (resolve_encode() != 0) return -1;
   RB200_CHECK(rank >= 1 && rank <= 5, "tensor map rank %d out of range", rank);
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.dtype = (int)dtype;
+  key.rank = rank;
+  key.swizzle = (int)swizzle;
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+    if (i + 1 < rank) key.strides[i] = strides_bytes[i];
+  }
+  MapEntry& slot = t_map_cache[hash_key(key) % kMapCacheSlots];
+  if (slot.valid && slot.key == key) {
+    *out = slot.map;
+    return 0;
+  }
+  if (resolve_encode() != 0) return -1;
   RB200_CHECK((reinterpret_cast<uintptr_t>(base) & 15u) == 0, "tensor map needs a 16-byte aligned base");
   cuuint64_t d[5];
   cuuint64_t st[4];
@@ -47,6 +90,9 @@ int make_tensor_map(CUtensorMap* out, const void* base, CUtensorMapDataType dtyp
                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RB200_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  slot.key = key;
+  slot.map = *out;
+  slot.valid = true;
   return 0;
 }
 

@@ -9,7 +9,7 @@
 namespace rb200 {
 
 static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count, const int64_t* indptr,
-                      int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, bool grouped,
+                      int indptr_has_prev, int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, bool grouped,
                       cudaStream_t stream) {
   using namespace um;
   // coverage: whole 128-row tiles, whole 64-k blocks, TMA-loadable x, 16-byte row stores
@@ -29,6 +29,7 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
   pp.g = p_in;
   GemvParams& p = pp.g;
   pp.indptr = indptr;
+  pp.indptr_has_prev = indptr_has_prev;
   pp.num_experts = num_experts;
   pp.w_expert_bytes = w_expert_bytes;
   pp.s_expert_stride = s_expert_stride;
@@ -119,13 +120,15 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
 }
 
 int umma_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, cudaStream_t stream) {
-  return run_common(p, bits, zmode, sm_count, nullptr, 1, 0, 0, false, stream);
+  return run_common(p, bits, zmode, sm_count, nullptr, 0, 1, 0, 0, false, stream);
 }
 
 int umma_group_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, const int64_t* indptr,
-                        int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, cudaStream_t stream) {
+                        int indptr_has_prev, int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride,
+                        cudaStream_t stream) {
   RB200_CHECK(indptr != nullptr, "indptr must be non-NULL");
-  return run_common(p, bits, zmode, sm_count, indptr, num_experts, w_expert_bytes, s_expert_stride, true, stream);
+  return run_common(p, bits, zmode, sm_count, indptr, indptr_has_prev, num_experts, w_expert_bytes, s_expert_stride, true,
+                    stream);
 }
 
 }  // namespace rb200

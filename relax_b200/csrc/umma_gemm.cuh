@@ -64,6 +64,7 @@ struct Params {
   // grouped form: rows [indptr[e-1], indptr[e]) of x / out belong to expert e (indptr: device,
   // end offsets); indptr == nullptr: one group holding all g.m rows
   const int64_t* indptr;
+  int indptr_has_prev;      // the first group starts at indptr[-1] (a sub-range of a longer table), not at row 0
   int num_experts;
   int64_t w_expert_bytes;   // bytes between experts' packed weights
   int64_t s_expert_stride;  // elements between experts' scale (and zero) tensors
@@ -265,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   const int n_tiles = p.n / kTileRows;
   if (tid < pp.num_experts) {
-    const int64_t r0 = pp.indptr ? (tid ? pp.indptr[tid - 1] : 0) : 0;
+    const int64_t r0 = pp.indptr ? ((tid || pp.indptr_has_prev) ? pp.indptr[tid - 1] : 0) : 0;
     int64_t r1 = pp.indptr ? pp.indptr[tid] : p.m;
     if (r1 > p.m) r1 = p.m;  // never past the rows x / out hold
     tt.row_begin[tid] = (int)r0;
@@ -700,6 +701,7 @@ int umma_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, cudaSt
 // [E, N, K]).  p.m = total rows of x / out; indptr = device int64[num_experts] of end offsets.
 // 0 on launch, -1 on error (shapes outside the kernel's coverage are errors here).
 int umma_group_gemm_run(const GemvParams& p, int bits, int zmode, int sm_count, const int64_t* indptr,
-                        int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride, cudaStream_t stream);
+                        int indptr_has_prev, int num_experts, int64_t w_expert_bytes, int64_t s_expert_stride,
+                        cudaStream_t stream);
 
 }  // namespace rb200

@@ -78,13 +78,21 @@ def group_gemm_fp16(x, weight, indptr, workspace=None, out: Optional[torch.Tenso
     return out
 
 
-def moe_gemm_ft(x, w_pre, scales, indptr, zeros=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def moe_gemm_ft(x, w_pre, scales, indptr, zeros=None, out: Optional[torch.Tensor] = None,
+                first_expert: int = 0) -> torch.Tensor:
     """Grouped decode-matmul over FT-layout experts: ``w_pre`` int8 [E, K, N/2] (int4) or
-    [E, K, N] (int8) from :func:`preprocess_weight_ft`, ``scales`` fp16 [E, K/g, N] or [E, N]."""
+    [E, K, N] (int8) from :func:`preprocess_weight_ft`, ``scales`` fp16 [E, K/g, N] or [E, N].
+    Expert-sharded layers: ``w_pre`` / ``scales`` hold experts ``first_expert ..`` only while
+    ``indptr`` is the whole layer's table; rows of other experts are left untouched in ``out``."""
     n = scales.shape[-1]
     if out is None:
         out = torch.empty(x.shape[0], n, dtype=torch.float16, device=x.device)
-    get_global_func("cutlass.moe_gemm")(x, w_pre, scales, zeros, indptr, None, out)
+    e_local = w_pre.shape[0]
+    if first_expert or e_local != indptr.shape[0]:
+        view = indptr[first_expert:first_expert + e_local]
+        get_global_func("cutlass.moe_gemm")(x, w_pre, scales, zeros, view, None, out, 1 if first_expert else 0)
+    else:
+        get_global_func("cutlass.moe_gemm")(x, w_pre, scales, zeros, indptr, None, out)
     return out
 
 

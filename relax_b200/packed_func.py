@@ -8,6 +8,7 @@ ints, floats, strings or None; the call launches on torch's current CUDA stream.
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Any, Callable, List
 
 import torch
@@ -67,12 +68,82 @@ def _cached_dltensor(t: torch.Tensor):
     return dl
 
 
+class _StreamMemo(threading.local):
+    """The stream this thread most recently handed to rb200_set_stream (thread local there too)."""
+    value = None
+
+
+_LAST_STREAM = _StreamMemo()
+
+
+class BoundCall:
+    """A PackedFunc call with its argument arrays built once (``PackedFunc.bind``): a serving loop
+    that passes the same buffers on every step pays for the ctypes marshalling only the first
+    time.  Calling it launches on torch's current stream of the current device."""
+
+    __slots__ = ("_fn", "_handle", "_values", "_codes", "_n", "_keep", "_ret", "_ret_code", "_set_stream", "_check")
+
+    def __init__(self, handle, values, codes, n, keep):
+        lib = _lib.load()
+        self._fn = lib.RB200FuncCall
+        self._set_stream = lib.rb200_set_stream
+        self._handle, self._values, self._codes, self._n, self._keep = handle, values, codes, n, keep
+        self._ret = Value()
+        self._ret_code = ctypes.c_int(ARG_NULL)
+        self._check = _lib.check
+
+    def __call__(self):
+        stream = torch.cuda.current_stream().cuda_stream
+        if _LAST_STREAM.value != stream:
+            self._set_stream(ctypes.c_void_p(stream))
+            _LAST_STREAM.value = stream
+        rc = self._fn(self._handle, self._values, self._codes, self._n, ctypes.byref(self._ret),
+                      ctypes.byref(self._ret_code))
+        if rc != 0:
+            self._check(rc)
+
+
 class PackedFunc:
     """One global function of the registry (what ``TVMFuncGetGlobal`` hands back)."""
 
     def __init__(self, name: str, handle: int):
         self.name = name
         self.handle = handle
+
+    def _marshal(self, args):
+        n = len(args)
+        values = (Value * max(n, 1))()
+        codes = (ctypes.c_int * max(n, 1))()
+        keep: List[Any] = []
+        for i, a in enumerate(args):
+            if a is None:
+                values[i].v_handle = None
+                codes[i] = ARG_NULL
+            elif isinstance(a, torch.Tensor):
+                dl = as_dltensor(a, keep)
+                keep.append(a)
+                values[i].v_handle = ctypes.addressof(dl)
+                codes[i] = ARG_DLTENSOR
+            elif isinstance(a, bool) or isinstance(a, int):
+                values[i].v_int64 = int(a)
+                codes[i] = ARG_INT
+            elif isinstance(a, float):
+                values[i].v_float64 = a
+                codes[i] = ARG_FLOAT
+            elif isinstance(a, str):
+                b = a.encode()
+                keep.append(b)
+                values[i].v_str = b
+                codes[i] = ARG_STR
+            else:
+                raise TypeError("unsupported PackedFunc argument %r" % type(a))
+        return values, codes, n, keep
+
+    def bind(self, *args: Any) -> BoundCall:
+        """Marshals ``args`` once; the returned object repeats the call (same tensors, same
+        scalars) with no per-call argument work.  The tensors are kept alive by the binding."""
+        values, codes, n, keep = self._marshal(args)
+        return BoundCall(self.handle, values, codes, n, keep)
 
     def __call__(self, *args: Any):
         lib = _lib.load()
@@ -110,11 +181,14 @@ class PackedFunc:
             cur = torch.cuda.current_device()
             dev_index = cur if cuda_dev is None or cuda_dev.index is None else cuda_dev.index
             if dev_index == cur:
-                lib.rb200_set_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                stream = torch.cuda.current_stream().cuda_stream
+                lib.rb200_set_stream(ctypes.c_void_p(stream))
+                _LAST_STREAM.value = stream
                 rc = lib.RB200FuncCall(self.handle, values, codes, n, ctypes.byref(ret),
                                        ctypes.byref(ret_code))
             else:
                 with torch.cuda.device(dev_index):
+                    _LAST_STREAM.value = None
                     lib.rb200_set_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
                     rc = lib.RB200FuncCall(self.handle, values, codes, n, ctypes.byref(ret),
                                            ctypes.byref(ret_code))

@@ -93,6 +93,119 @@ def allreduce_sum_(t, group=None):
     return t
 
 
+class PeerWorkspace:
+    """A zero-filled device buffer of this rank that every rank of the group can address: allocated
+    with ``rb200_peer_alloc``, its CUDA IPC handle exchanged over ``torch.distributed`` (host bytes
+    only, any backend) and the peers' handles mapped - what
+    src/runtime/disco/cuda_ipc/cuda_ipc_memory.cc does over Disco's channel.  ``ptrs[p]`` is this
+    process's address of rank p's buffer."""
+
+    def __init__(self, nbytes: int, group=None):
+        import ctypes
+        import torch.distributed as dist
+        from . import _lib
+        self._lib = _lib
+        lib = _lib.load()
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one node)")
+        own = ctypes.c_void_p()
+        _lib.check(lib.rb200_peer_alloc(nbytes, ctypes.byref(own)))
+        self._own = own
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.rb200_peer_export(own, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._imported = []
+        self.ptrs = (ctypes.c_void_p * self.world)()
+        for p in range(self.world):
+            if p == self.rank:
+                self.ptrs[p] = own.value
+            else:
+                q = ctypes.c_void_p()
+                _lib.check(lib.rb200_peer_import(ctypes.create_string_buffer(handles[p], 64), ctypes.byref(q)))
+                self._imported.append(q)
+                self.ptrs[p] = q.value
+        dist.barrier(group=group)  # every workspace exists and is zero before the first use
+
+    def close(self):
+        lib = self._lib.load()
+        for q in self._imported:
+            lib.rb200_peer_close(q)
+        self._imported = []
+        if self._own is not None:
+            lib.rb200_peer_free(self._own)
+            self._own = None
+
+
+class RowParallelLinear:
+    """Row-parallel decode matmul whose epilogue is the all-reduce (``rb200_gemm_fp16_intx_allreduce``):
+    one kernel per rank instead of the reference's matmul followed by ``runtime.disco.allreduce``
+    (src/runtime/disco/nccl/nccl.cc:90-98).  One object serves every row-parallel layer of a model
+    whose output width is at most ``max_n``; calls must be issued in the same order on all ranks."""
+
+    def __init__(self, max_n: int, group=None):
+        from . import _lib
+        self._lib = _lib
+        self.max_n = int(max_n)
+        self.ws = PeerWorkspace(_lib.load().rb200_gemm_allreduce_workspace_bytes(self.max_n), group)
+        self.rank, self.world = self.ws.rank, self.ws.world
+
+    def _call(self, d):
+        import ctypes
+        import torch
+        lib = self._lib.load()
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self._lib.check(lib.rb200_gemm_fp16_intx_allreduce(ctypes.byref(d), self.ws.ptrs, self.rank, self.world,
+                                                           self.max_n, stream))
+
+    def gemm_q4f16(self, x, w_pre, scales, out, group_size: int = 32, zero_const: float = 7.0, bias=None,
+                   residual=None, activation: int = 0):
+        """``out = epilogue(sum over ranks of x_shard @ decode(w_shard)^T)`` for q4f16_1 shards
+        (:func:`shard_q4f16` with ``axis="k"``), every rank receiving the full result."""
+        import ctypes
+        d = self._lib.GemmDesc()
+        d.struct_size = ctypes.sizeof(self._lib.GemmDesc)
+        d.weight_bits = 4
+        k = x.shape[-1]
+        d.x, d.w, d.scales, d.out = x.data_ptr(), w_pre.data_ptr(), scales.data_ptr(), out.data_ptr()
+        d.m, d.n, d.k = x.numel() // k, w_pre.shape[0], k
+        d.ldx, d.ldo = k, w_pre.shape[0]
+        d.group_size = group_size
+        d.scale_stride_n, d.scale_stride_g = k // group_size, 1
+        d.zero_const = zero_const
+        d.activation = activation
+        if bias is not None:
+            d.bias = bias.data_ptr()
+        if residual is not None:
+            d.residual, d.binary_op = residual.data_ptr(), 1
+        self._call(d)
+        return out
+
+    def gemm_ft(self, x, w_pre, scales, weight_bits: int, out, bias=None):
+        """The same for FT-layout shards with per-channel scales (:func:`shard_ft` with ``axis="k"``)."""
+        import ctypes
+        d = self._lib.GemmDesc()
+        d.struct_size = ctypes.sizeof(self._lib.GemmDesc)
+        d.weight_bits = weight_bits
+        k = x.shape[-1]
+        n = w_pre.shape[-1] * (2 if weight_bits == 4 else 1)
+        d.x, d.w, d.scales, d.out = x.data_ptr(), w_pre.data_ptr(), scales.data_ptr(), out.data_ptr()
+        d.m, d.n, d.k = x.numel() // k, n, k
+        d.ldx, d.ldo = k, n
+        d.group_size = k
+        d.scale_stride_n, d.scale_stride_g = 1, 0
+        d.zero_const = 8.0 if weight_bits == 4 else 128.0
+        if bias is not None:
+            d.bias = bias.data_ptr()
+        self._call(d)
+        return out
+
+    def close(self):
+        self.ws.close()
+
+
 class OneShotAllReduce:
     """Low-latency sum all-reduce of small fp16 tensors between the GPUs of one node
     (``rb200_allreduce_oneshot``): the counterpart of ``runtime.disco.cuda_ipc.custom_allreduce``
@@ -106,38 +219,14 @@ class OneShotAllReduce:
     All ranks must call with the same sequence of tensor sizes."""
 
     def __init__(self, max_count: int, group=None):
-        import ctypes
         import torch
-        import torch.distributed as dist
         from . import _lib
         self._lib = _lib
-        lib = _lib.load()
         self.group = group
-        self.rank = dist.get_rank(group)
-        self.world = dist.get_world_size(group)
-        if self.world > 8:
-            raise ValueError("at most 8 ranks (one node)")
         self.max_count = int(max_count)
-        nbytes = lib.rb200_allreduce_workspace_bytes(self.max_count)
-        own = ctypes.c_void_p()
-        _lib.check(lib.rb200_peer_alloc(nbytes, ctypes.byref(own)))
-        self._own = own
-        handle = ctypes.create_string_buffer(64)
-        _lib.check(lib.rb200_peer_export(own, handle))
-        handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle.raw), group=group)
-        self._imported = []
-        ptrs = (ctypes.c_void_p * self.world)()
-        for p in range(self.world):
-            if p == self.rank:
-                ptrs[p] = own.value
-            else:
-                q = ctypes.c_void_p()
-                _lib.check(lib.rb200_peer_import(ctypes.create_string_buffer(handles[p], 64), ctypes.byref(q)))
-                self._imported.append(q)
-                ptrs[p] = q.value
-        self._ptrs = ptrs
-        dist.barrier(group=group)  # every workspace exists and is zero before the first call
+        self.ws = PeerWorkspace(_lib.load().rb200_allreduce_workspace_bytes(self.max_count), group)
+        self.rank, self.world = self.ws.rank, self.ws.world
+        self._ptrs = self.ws.ptrs
         self._torch = torch
 
     def fits(self, t) -> bool:
@@ -157,10 +246,4 @@ class OneShotAllReduce:
         return out
 
     def close(self):
-        lib = self._lib.load()
-        for q in self._imported:
-            lib.rb200_peer_close(q)
-        self._imported = []
-        if self._own is not None:
-            lib.rb200_peer_free(self._own)
-            self._own = None
+        self.ws.close()
