@@ -209,12 +209,261 @@ class ClockSampler:
         return out
 
 
+def _events():
+    import torch
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def graph_time(fn, calls=8, reps=3, allow_graph=True):
+    """ms per call of `fn`: `calls` back-to-back calls captured in a CUDA graph (so that no host time
+    is in the figure), `reps` replays between two events; eager launches when capture is refused."""
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    g_ = None
+    if allow_graph:
+        try:
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_):
+                for _ in range(calls):
+                    fn()
+            g_.replay()
+        except Exception:
+            g_ = None
+        torch.cuda.synchronize()
+    a_, b_ = _events()
+    a_.record()
+    for _ in range(reps):
+        if g_ is not None:
+            g_.replay()
+        else:
+            for _ in range(calls):
+                fn()
+    b_.record()
+    torch.cuda.synchronize()
+    return a_.elapsed_time(b_) / (calls * reps)
+
+
+def max_over_ranks(v, world, dev):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return v
+    t = torch.tensor([v], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+# --------------------------------------------------------------------------- sharded configurations (N > 1 and N = 1)
+def llama70b_mlp_block(world, rank, dev, rp, barrier):
+    """Configuration 3 as it is deployed: gate_up (8192 -> 2 x 28672, int8 per channel) column-parallel
+    with the gated activation fused, down (28672 -> 8192) row-parallel, then the sum over ranks -
+    fused into the down matmul's epilogue at M <= 32, NCCL for the megabyte-sized messages above.
+    Every rank also times the unsharded MLP, which is the strong-scaling denominator."""
+    import torch
+    import torch.distributed as dist
+    from relax_b200 import ops
+    K, F = 8192, 28672
+
+    def gen_shard(r, w):  # (gate_up [K, 2F/w] = [gate_r | up_r], its scales, down [F/w, K], its scales)
+        g = torch.Generator(device=dev)
+        g.manual_seed(30000 + 97 * w + r)
+        fl = F // w
+        gu = torch.randint(-127, 128, (K, 2 * fl), dtype=torch.int8, device=dev, generator=g)
+        gus = (torch.rand((2 * fl,), device=dev, generator=g) * 0.0009 + 0.0001).half()
+        dn = torch.randint(-127, 128, (fl, K), dtype=torch.int8, device=dev, generator=g)
+        dns = (torch.rand((K,), device=dev, generator=g) * 0.0009 + 0.0001).half()
+        return gu, gus, dn, dns
+
+    def prep(gu, gus, dn, dns):
+        return (ops.preprocess_weight_gate_up(gu, ops.LAYOUT_FT_KN, False), ops.interleave_gate_up(gus, 0),
+                ops.preprocess_weight_ft(dn, False), dns)
+
+    out = {}
+    full = prep(*gen_shard(0, 1))
+    mine_raw = gen_shard(rank, world) if world > 1 else None
+    mine = prep(*mine_raw) if world > 1 else full
+    gx = torch.Generator(device=dev)
+    gx.manual_seed(31000)
+    for m in (16, 256, 4096):
+        x = torch.randn((m, K), device=dev, generator=gx).half()
+        h_full = torch.empty((m, F), dtype=torch.float16, device=dev)
+        o_full = torch.empty((m, K), dtype=torch.float16, device=dev)
+
+        def mlp_full():
+            ops.gemm_fp16_ft(x, full[0], full[1], 8, activation="swiglu", out=h_full)
+            ops.gemm_fp16_ft(h_full, full[2], full[3], 8, out=o_full)
+
+        calls = 2 if m >= 4096 else 6
+        t1 = max_over_ranks(graph_time(mlp_full, calls=calls), world, dev)
+        flops = 2.0 * m * K * 2 * F + 2.0 * m * F * K
+        entry = {"unsharded_us": t1 * 1e3, "unsharded_tflops": flops / (t1 * 1e-3) / 1e12,
+                 "unsharded_weight_gbs": 3.0 * K * F / (t1 * 1e-3) / 1e9}
+        if world > 1:
+            fl = F // world
+            h = torch.empty((m, fl), dtype=torch.float16, device=dev)
+            o = torch.empty((m, K), dtype=torch.float16, device=dev)
+            fused = m <= 32
+
+            def mlp_tp():
+                ops.gemm_fp16_ft(x, mine[0], mine[1], 8, activation="swiglu", out=h)
+                if fused:
+                    rp.gemm_ft(h, mine[2], mine[3], 8, o)
+                else:
+                    ops.gemm_fp16_ft(h, mine[2], mine[3], 8, out=o)
+                    dist.all_reduce(o)
+
+            barrier()
+            tn = max_over_ranks(graph_time(mlp_tp, calls=calls), world, dev)
+            entry.update({"us": tn * 1e3, "tflops_per_gpu": flops / world / (tn * 1e-3) / 1e12,
+                          "weight_gbs_per_gpu": 3.0 * K * F / world / (tn * 1e-3) / 1e9,
+                          "speedup_over_unsharded": t1 / tn, "strong_scaling_efficiency": t1 / tn / world,
+                          "allreduce": "fused into the down matmul's epilogue" if fused else "nccl"})
+            # parity of rank 0's output against the oracle on a row sample (all shards regenerated on rank 0)
+            if m in (16, 256):
+                mlp_tp()
+                torch.cuda.synchronize()
+                barrier()
+                if rank == 0:
+                    from oracle import oracle as orc
+                    C = orc.C()
+                    rows = [0, m // 2, m - 1]
+                    xs_ = x[rows].cpu().numpy()
+                    acc = np.zeros((len(rows), K), dtype=np.float32)
+                    for r in range(world):
+                        gu, gus, dn, dns = gen_shard(r, world)
+                        a1 = C.matmul_f32(xs_, C.decode_ft_kn(gu.cpu().numpy(), gus.cpu().numpy(), 8, -1), False)
+                        gate, up = a1[:, :fl].astype(np.float64), a1[:, fl:].astype(np.float64)
+                        hh = (gate / (1.0 + np.exp(-gate)) * up).astype(np.float16)
+                        acc += C.matmul_f32(hh, C.decode_ft_kn(dn.cpu().numpy(), dns.cpu().numpy(), 8, -1), False)
+                        del gu, gus, dn, dns
+                    exp = acc.astype(np.float16).astype(np.float32)
+                    got = o[rows].float().cpu().numpy()
+                    entry["max_rel_err_vs_oracle"] = float(np.max(np.abs(got - exp)) / max(np.max(np.abs(exp)), 1e-9))
+                barrier()
+            del h, o
+        out["m%d" % m] = entry
+        del x, h_full, o_full
+    return out
+
+
+def mixtral_block(world, rank, dev, barrier):
+    """Configuration 4 with the experts split over the ranks: route (softmax, top-2 of 8) -> gather ->
+    grouped matmul 4096 -> 14336 over this rank's experts -> grouped matmul 14336 -> 4096 -> weighted
+    combine -> sum over ranks of the [512, 4096] result (NCCL: 4 MiB).  W4 group 128, 512 tokens."""
+    import torch
+    import torch.distributed as dist
+    from relax_b200 import ops
+    from relax_b200.sharding import expert_range
+    T, H, F, E, G = 512, 4096, 14336, 8, 128
+
+    def gen_expert(e):
+        g = torch.Generator(device=dev)
+        g.manual_seed(40000 + e)
+        w1 = torch.randint(-128, 128, (H, F // 2), dtype=torch.int8, device=dev, generator=g)
+        s1 = (torch.rand((H // G, F), device=dev, generator=g) * 0.009 + 0.001).half()
+        w2 = torch.randint(-128, 128, (F, H // 2), dtype=torch.int8, device=dev, generator=g)
+        s2 = (torch.rand((F // G, H), device=dev, generator=g) * 0.0009 + 0.0001).half()
+        return w1, s1, w2, s2
+
+    e0, e1 = expert_range(E, rank, world)
+    parts = [gen_expert(e) for e in range(e0, e1)]
+    w1 = ops.preprocess_weight_ft(torch.stack([p_[0] for p_ in parts]), True)
+    s1 = torch.stack([p_[1] for p_ in parts]).contiguous()
+    w2 = ops.preprocess_weight_ft(torch.stack([p_[2] for p_ in parts]), True)
+    s2 = torch.stack([p_[3] for p_ in parts]).contiguous()
+    del parts
+    g = torch.Generator(device=dev)
+    g.manual_seed(41000)
+    logits = torch.randn((T, E), device=dev, generator=g)
+    x = torch.randn((T, H), device=dev, generator=g).half()
+    y1 = torch.empty((2 * T, F), dtype=torch.float16, device=dev)
+    y2 = torch.zeros((2 * T, H), dtype=torch.float16, device=dev)
+    holder = {}
+
+    def layer():
+        indptr, tok, gate, rof = ops.moe_route(logits, 2)
+        xg = ops.moe_gather(x, tok)
+        ops.moe_gemm_ft(xg, w1, s1, indptr, out=y1, first_expert=e0)
+        if world > 1:
+            y2.zero_()  # rows of the other ranks' experts contribute nothing to this rank's partial sum
+        ops.moe_gemm_ft(y1, w2, s2, indptr, out=y2, first_expert=e0)
+        res = ops.moe_combine(y2, rof, gate, 2)
+        if world > 1:
+            dist.all_reduce(res)
+        holder["res"], holder["route"] = res, (indptr, tok, gate, rof)
+
+    layer()
+    torch.cuda.synchronize()
+    barrier()
+    t = max_over_ranks(graph_time(layer, calls=4, allow_graph=False), world, dev)
+    flops = 2.0 * 2 * T * H * F * 2
+    entry = {"us": t * 1e3, "tflops_total": flops / (t * 1e-3) / 1e12, "experts_per_rank": e1 - e0,
+             "timed_with": "eager launches (the routing step allocates its outputs)",
+             "allreduce": "nccl [512, 4096] fp16" if world > 1 else "none"}
+    # parity: a few tokens against the oracle (their two experts regenerated on rank 0)
+    layer()
+    torch.cuda.synchronize()
+    if rank == 0:
+        from oracle import oracle as orc
+        C = orc.C()
+        p = torch.softmax(logits, dim=1).cpu().numpy()
+        xs_ = x.cpu().numpy()
+        got = holder["res"].float().cpu().numpy()
+        worst = 0.0
+        for tkn in (0, 255, 511):
+            order = np.argsort(-p[tkn], kind="stable")[:2]
+            partial = {}
+            for e in order:
+                w1e, s1e, w2e, s2e = gen_expert(int(e))
+                a1 = C.epilogue(C.matmul_f32(xs_[tkn:tkn + 1], C.decode_ft_kn(w1e.cpu().numpy(), s1e.cpu().numpy(), 4, G), False))
+                a2 = C.epilogue(C.matmul_f32(a1, C.decode_ft_kn(w2e.cpu().numpy(), s2e.cpu().numpy(), 4, G), False))
+                owner = int(e) // (E // world)
+                partial[owner] = partial.get(owner, 0.0) + np.float32(p[tkn, e]) * a2.astype(np.float32)
+            exp = sum(v.astype(np.float16).astype(np.float32) for v in partial.values())
+            worst = max(worst, float(np.max(np.abs(got[tkn] - exp[0])) / max(np.max(np.abs(exp)), 1e-9)))
+        entry["max_rel_err_vs_oracle"] = worst
+    barrier()
+    return entry
+
+
+def preprocess_block(dev, peak):
+    """The one-time repack at the three sizes the configurations use: microseconds and fraction of
+    the copy peak (every byte read once and written once)."""
+    import torch
+    from relax_b200 import ops
+    g = torch.Generator(device=dev)
+    g.manual_seed(5000)
+    out = {}
+    cases = [("q4f16_1_gate_up_45MB", lambda: torch.randint(-2 ** 31, 2 ** 31 - 1, (22016, 512), dtype=torch.int32, device=dev, generator=g),
+              lambda w: ops.preprocess_weight_q4f16(w)),
+             ("ft_int8_gate_up_470MB", lambda: torch.randint(-127, 128, (8192, 57344), dtype=torch.int8, device=dev, generator=g),
+              lambda w: ops.preprocess_weight_ft(w, False)),
+             ("ft_int4_experts_235MB", lambda: torch.randint(-128, 128, (8, 4096, 7168), dtype=torch.int8, device=dev, generator=g),
+              lambda w: ops.preprocess_weight_ft(w, True))]
+    for name, make, run in cases:
+        copies = [make() for _ in range(4 if "45MB" in name else 2)]
+        nbytes = copies[0].numel() * copies[0].element_size()
+        state = {"i": 0}
+
+        def one():
+            run(copies[state["i"] % len(copies)])
+            state["i"] += 1
+
+        ms = graph_time(one, calls=len(copies), reps=3, allow_graph=False)
+        out[name] = {"us": ms * 1e3, "gbs": 2.0 * nbytes / (ms * 1e-3) / 1e9, "frac_of_copy_peak": 2.0 * nbytes / (ms * 1e-3) / 1e9 / peak}
+        del copies
+    return out
+
+
+# --------------------------------------------------------------------------- GPU arm
 def run_gpu(args):
     import torch
     import torch.distributed as dist
 
     import relax_b200
     from relax_b200 import ops, synth
+    from relax_b200.packed_func import get_global_func
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -222,26 +471,33 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # the all-reduced messages are at most 256 KiB: plain peer transfers, no NVLink multicast
-        # bindings to unwind at tear-down
+        # plain peer transfers everywhere: no NVLink multicast bindings to unwind at tear-down
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     # serving-loop setting: weights are resident and never rewritten, so consecutive decode kernels
     # may overlap their launch and weight streaming with the previous kernel's tail
     relax_b200.set_launch_overlap(os.environ.get("RB200_BENCH_NO_OVERLAP", "0") != "1")
 
-    # row-parallel outputs ([M, 4096] fp16, at most 256 KiB): NCCL by default; RB200_BENCH_ONESHOT_ALLREDUCE=1
-    # uses the library's one-shot all-reduce over CUDA IPC workspaces instead
-    allreduce = None
-    allreduce_kind = "none"
+    # row-parallel outputs ([M, 4096] fp16, at most 256 KiB): the sum over ranks is the epilogue of
+    # the matmul kernel itself; RB200_BENCH_ALLREDUCE=nccl / oneshot select a separate collective
+    ar_mode = os.environ.get("RB200_BENCH_ALLREDUCE", "fused") if world > 1 else "none"
+    rp = None
+    separate_ar = None
     if world > 1:
-        allreduce_kind = "nccl"
-        allreduce = lambda t: dist.all_reduce(t)
-        if os.environ.get("RB200_BENCH_ONESHOT_ALLREDUCE", "0") == "1":
-            from relax_b200.sharding import OneShotAllReduce
-            allreduce = OneShotAllReduce(max(MS) * 4096)
-            allreduce_kind = "one-shot (rb200_allreduce_oneshot)"
+        from relax_b200.sharding import OneShotAllReduce, RowParallelLinear
+        rp = RowParallelLinear(8192)
+        if ar_mode == "nccl":
+            separate_ar = lambda t: dist.all_reduce(t)
+        elif ar_mode == "oneshot":
+            separate_ar = OneShotAllReduce(max(MS) * 4096)
+    ar_names = {"fused": "fused into the row-parallel matmul's epilogue (rb200_gemm_fp16_intx_allreduce)",
+                "nccl": "nccl", "oneshot": "one-shot kernel (rb200_allreduce_oneshot)", "none": "none"}
 
     gen = torch.Generator(device=dev)
     gen.manual_seed(1000 + rank)
@@ -258,12 +514,21 @@ def run_gpu(args):
             layer[name] = (ops.preprocess_weight_q4f16(w), sc, w if s_i == 0 else None)
             del w
         sets.append(layer)
-    xs = {(name, m): torch.randn((m, k), device=dev, generator=gen).to(torch.float16)
-          for name, k, n in lin for m in MS}
-    outs = {(name, m): torch.empty((m, n), dtype=torch.float16, device=dev) for name, k, n in lin for m in MS}
+    # activations and results live in two contiguous device buffers (one host copy each way per step)
+    keys = [(name, m) for m in MS for name, k, n in lin]
+    dims = {name: (k, n) for name, k, n in lin}
+    x_all = torch.randn(sum(m * dims[name][0] for name, m in keys), device=dev, generator=gen).to(torch.float16)
+    o_all = torch.empty(sum(m * dims[name][1] for name, m in keys), dtype=torch.float16, device=dev)
+    xs, outs, xo, oo = {}, {}, 0, 0
+    for name, m in keys:
+        k, n = dims[name]
+        xs[(name, m)] = x_all[xo:xo + m * k].view(m, k)
+        outs[(name, m)] = o_all[oo:oo + m * n].view(m, n)
+        xo += m * k
+        oo += m * n
     torch.cuda.synchronize()
 
-    # ---- parity spot check against the CPU oracle (rank 0, one linear, a row sample)
+    # ---- parity spot check against the CPU oracle (rank 0, one linear, a column sample)
     max_rel_err = None
     if rank == 0:
         from oracle import oracle as orc
@@ -279,45 +544,42 @@ def run_gpu(args):
         for name in layer:
             layer[name] = layer[name][:2]
 
+    # ---- the 12 calls of a step, argument arrays built once per (weight set, linear, M)
+    gemm = get_global_func("relax_b200.gemm_fp16_q4f16")
+    bound = {}
+    for s_i, layer in enumerate(sets):
+        for name, m in keys:
+            pre, sc = layer[name]
+            if world > 1 and name in row_parallel and ar_mode == "fused":
+                bound[(s_i, name, m)] = rp.bind_q4f16(xs[(name, m)], pre, sc, outs[(name, m)], GROUP, 7.0)
+            else:
+                bound[(s_i, name, m)] = gemm.bind(xs[(name, m)], pre, sc, None, None, None, "identity", "", "identity",
+                                                  GROUP, 7.0, outs[(name, m)])
     counter = {"launches": 0}
 
-    def one_step(step_idx, events=None):
+    def one_step(step_idx):
         for mi, m in enumerate(MS):
-            layer = sets[(step_idx * len(MS) + mi) % WEIGHT_SETS]
+            s_i = (step_idx * len(MS) + mi) % WEIGHT_SETS
             for name, k, n in lin:
-                pre, sc = layer[name]
-                if events is not None:
-                    e0 = torch.cuda.Event(enable_timing=True)
-                    e1 = torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                ops.gemm_fp16_q4f16(xs[(name, m)], pre, sc, out=outs[(name, m)])
+                bound[(s_i, name, m)]()
                 counter["launches"] += 1
-                if events is not None:
-                    e1.record()
-                    events.append((e0, e1, synth.algorithmic_bytes(m, n, k, 4, GROUP)))
-                if world > 1 and name in row_parallel:
-                    allreduce(outs[(name, m)])
+                if separate_ar is not None and name in row_parallel:
+                    separate_ar(outs[(name, m)])
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing: the step is launch-bound from Python (kernels of 3-12 us), so
+    # ---- device-resident timing: the step is launch-bound from Python (kernels of 8-30 us), so
     # each of the WEIGHT_SETS rotation phases is captured once in a CUDA graph and replayed
     for i in range(max(args.warmup, WEIGHT_SETS)):
         one_step(i)
     barrier()
     graphs = []
-    use_graphs = os.environ.get("RB200_BENCH_NO_GRAPH", "0") != "1"
-    if use_graphs:
+    if os.environ.get("RB200_BENCH_NO_GRAPH", "0") != "1":
         try:
             for ph in range(WEIGHT_SETS):
                 g_ = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g_):
                     one_step(ph)
                 graphs.append(g_)
-        except Exception as exc:  # capture of the collective refused: time eager launches instead
+        except Exception as exc:  # capture of a collective refused: time eager launches instead
             if rank == 0:
                 sys.stderr.write("graph capture unavailable (%s); timing eager launches\n" % exc)
             graphs = []
@@ -336,8 +598,7 @@ def run_gpu(args):
     clocks = ClockSampler(local)
     clocks.start()
     counter["launches"] = 0
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
+    t0, t1 = _events()
     barrier()
     t0.record()
     for i in range(args.steps):
@@ -346,6 +607,30 @@ def run_gpu(args):
     barrier()
     ms_total = t0.elapsed_time(t1)
     launches = counter["launches"]
+
+    # ---- end-to-end timing through the PackedFunc surface with host buffers: every step copies
+    # its activations from pinned host memory, runs the 12 calls and reads the 12 results back
+    hx = x_all.cpu().pin_memory()
+    hout = torch.empty_like(o_all, device="cpu").pin_memory()
+    h2d, d2h = hx.numel() * 2, hout.numel() * 2
+
+    def e2e_step(step_idx):
+        x_all.copy_(hx, non_blocking=True)
+        one_step(step_idx)
+        hout.copy_(o_all, non_blocking=True)
+        torch.cuda.synchronize()  # the step's results are on the host
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    e0, e1 = _events()
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(args.warmup + i)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clk = clocks.stop()
 
     # ---- per-shape roofline pass: for every (linear, M) a CUDA graph of back-to-back launches
     # over enough distinct weight copies to exceed L2 (>= 320 MB per shape), CUDA events around
@@ -359,31 +644,21 @@ def run_gpu(args):
         scs = [sc0.clone() for _ in range(copies)]
         torch.cuda.synchronize()  # weights are complete before any overlapped launch reads them
         for m in MS:
-            def run_all():
-                for c_ in range(copies):
-                    ops.gemm_fp16_q4f16(xs[(name, m)], pres[c_], scs[c_], out=outs[(name, m)])
-            run_all()
-            torch.cuda.synchronize()
-            g_ = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_):
-                run_all()
-            g_.replay()
-            torch.cuda.synchronize()
-            reps = 3
-            a_ = torch.cuda.Event(enable_timing=True)
-            b_ = torch.cuda.Event(enable_timing=True)
-            a_.record()
-            for _ in range(reps):
-                g_.replay()
-            b_.record()
-            torch.cuda.synchronize()
-            per_shape["%s_m%d" % (name, m)] = (a_.elapsed_time(b_) / (reps * copies),
+            calls = [gemm.bind(xs[(name, m)], pres[c_], scs[c_], None, None, None, "identity", "", "identity",
+                               GROUP, 7.0, outs[(name, m)]) for c_ in range(copies)]
+            state = {"i": 0}
+
+            def run_one():
+                calls[state["i"] % copies]()
+                state["i"] += 1
+
+            per_shape["%s_m%d" % (name, m)] = (graph_time(run_one, calls=copies, reps=3),
                                                synth.algorithmic_bytes(m, n, k, 4, GROUP))
-            del g_
         del pres, scs
     achieved = sum(c for _, c in per_shape.values()) / (sum(t for t, _ in per_shape.values()) * 1e-3) / 1e9
     shape_gbs = {k_: round(c / (t * 1e-3) / 1e9, 1) for k_, (t, c) in per_shape.items()}
     shape_us = {k_: round(t * 1e3, 2) for k_, (t, c) in per_shape.items()}
+    peak, peak_kind = measured_peak()
 
     # ---- secondary figure: the prefill configuration (m 2048, k 4096, n 22016, group 128 with
     # zero points) on the tcgen05 kernel, against the measured dense-fp16 tensor peak
@@ -402,8 +677,7 @@ def run_gpu(args):
             ops.gemm_fp16_q4f16(px, pw, ps, pz, group_size=128, out=po)
         torch.cuda.synchronize()
         reps = 20
-        a_ = torch.cuda.Event(enable_timing=True)
-        b_ = torch.cuda.Event(enable_timing=True)
+        a_, b_ = _events()
         a_.record()
         for _ in range(reps):
             ops.gemm_fp16_q4f16(px, pw, ps, pz, group_size=128, out=po)
@@ -411,10 +685,8 @@ def run_gpu(args):
         torch.cuda.synchronize()
         pt = a_.elapsed_time(b_) / reps
         tf = 2.0 * pm * pk * pn / (pt * 1e-3) / 1e12
-        tpeak = None
         try:
-            tpeak = float(json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)),
-                                                      "MEASURED_PEAKS.json")))["bf16_tflops"])
+            tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
         except Exception:
             tpeak = 1590.0
         prefill = {"workload": "W4A16 group-128 asymmetric GEMM m=2048 k=4096 n=22016", "kernel": "umma_gemm_kernel",
@@ -422,89 +694,44 @@ def run_gpu(args):
                    "l2": "x + packed weight + out = 152 MB per launch, larger than L2"}
         del pw, ps, pz, px, po
 
-    # ---- further secondary figures (single GPU): the other configurations' shapes, graph-timed
+    # ---- the other configurations.  Single GPU: their shard shapes and the Mixtral layer, graph-timed.
+    # Every N (1 included): the sharded Llama-70B MLP and the expert-sharded Mixtral layer.
     extra = None
-    if world == 1 and os.environ.get("RB200_BENCH_NO_EXTRA", "0") != "1":
+    if os.environ.get("RB200_BENCH_NO_EXTRA", "0") != "1":
         extra = {}
-
-        def graph_time(fn, calls=8, reps=3):
-            fn()
+        if world == 1:
+            gen2 = torch.Generator(device=dev)
+            gen2.manual_seed(3000)
+            for name, k3, n3 in (("gate_up_shard", 8192, 7168), ("down_shard", 3584, 8192)):
+                w8 = ops.preprocess_weight_ft(torch.randint(-127, 128, (k3, n3), dtype=torch.int8, device=dev,
+                                                            generator=gen2), False)
+                s8 = (torch.rand((n3,), device=dev, generator=gen2) * 0.0009 + 0.0001).half()
+                for m3 in (16, 256, 4096):
+                    x3 = torch.randn((m3, k3), device=dev, generator=gen2).half()
+                    o3 = torch.empty((m3, n3), device=dev, dtype=torch.float16)
+                    torch.cuda.synchronize()
+                    ms = graph_time(lambda: ops.gemm_fp16_ft(x3, w8, s8, 8, out=o3), calls=4 if m3 >= 4096 else 8)
+                    extra["llama70b_int8_%s_m%d" % (name, m3)] = {
+                        "us": ms * 1e3, "tflops": 2.0 * m3 * k3 * n3 / (ms * 1e-3) / 1e12,
+                        "weight_gbs": k3 * n3 / (ms * 1e-3) / 1e9}
+                del w8, s8
+            e4, k4, n4 = 8, 4096, 14336
+            logits = torch.randn((512, e4), device=dev, generator=gen2)
+            indptr4, tok4, gate4, rof4 = ops.moe_route(logits, 2)
+            w4 = ops.preprocess_weight_ft(torch.randint(-128, 128, (e4, k4, n4 // 2), dtype=torch.int8, device=dev,
+                                                        generator=gen2), True)
+            s4 = (torch.rand((e4, k4 // 128, n4), device=dev, generator=gen2) * 0.009 + 0.001).half()
+            x4 = torch.randn((1024, k4), device=dev, generator=gen2).half()
+            o4 = torch.empty((1024, n4), device=dev, dtype=torch.float16)
             torch.cuda.synchronize()
-            g_ = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_):
-                for _ in range(calls):
-                    fn()
-            g_.replay()
-            torch.cuda.synchronize()
-            a_ = torch.cuda.Event(enable_timing=True)
-            b_ = torch.cuda.Event(enable_timing=True)
-            a_.record()
-            for _ in range(reps):
-                g_.replay()
-            b_.record()
-            torch.cuda.synchronize()
-            return a_.elapsed_time(b_) / (calls * reps)  # ms per call
-
-        gen2 = torch.Generator(device=dev)
-        gen2.manual_seed(3000)
-        # Llama-70B MLP, int8 per channel, 1/8 shards (gate_up column-parallel, down row-parallel)
-        for name, k3, n3 in (("gate_up_shard", 8192, 7168), ("down_shard", 3584, 8192)):
-            w8 = ops.preprocess_weight_ft(torch.randint(-127, 128, (k3, n3), dtype=torch.int8, device=dev,
-                                                        generator=gen2), False)
-            s8 = (torch.rand((n3,), device=dev, generator=gen2) * 0.0009 + 0.0001).half()
-            for m3 in (16, 256, 4096):
-                x3 = torch.randn((m3, k3), device=dev, generator=gen2).half()
-                o3 = torch.empty((m3, n3), device=dev, dtype=torch.float16)
-                torch.cuda.synchronize()
-                ms = graph_time(lambda: ops.gemm_fp16_ft(x3, w8, s8, 8, out=o3), calls=4 if m3 >= 4096 else 8)
-                extra["llama70b_int8_%s_m%d" % (name, m3)] = {
-                    "us": ms * 1e3, "tflops": 2.0 * m3 * k3 * n3 / (ms * 1e-3) / 1e12,
-                    "weight_gbs": k3 * n3 / (ms * 1e-3) / 1e9}
-            del w8, s8
-        # Mixtral expert layer: 512 tokens, top-2 of 8 experts, W4 group 128 (rows already sorted)
-        e4, k4, n4 = 8, 4096, 14336
-        logits = torch.randn((512, e4), device=dev, generator=gen2)
-        indptr4, tok4, gate4, rof4 = ops.moe_route(logits, 2)
-        w4 = ops.preprocess_weight_ft(torch.randint(-128, 128, (e4, k4, n4 // 2), dtype=torch.int8, device=dev,
-                                                    generator=gen2), True)
-        s4 = (torch.rand((e4, k4 // 128, n4), device=dev, generator=gen2) * 0.009 + 0.001).half()
-        x4 = torch.randn((1024, k4), device=dev, generator=gen2).half()
-        o4 = torch.empty((1024, n4), device=dev, dtype=torch.float16)
-        torch.cuda.synchronize()
-        ms = graph_time(lambda: ops.moe_gemm_ft(x4, w4, s4, indptr4, out=o4), calls=4)
-        extra["mixtral_moe_w4_g128_1024rows"] = {"us": ms * 1e3, "tflops": 2.0 * 1024 * k4 * n4 / (ms * 1e-3) / 1e12}
-        del w4, s4, x4, o4
-
-    # ---- end-to-end timing through the PackedFunc surface with host buffers
-    hx = {key: t.cpu().pin_memory() for key, t in xs.items()}
-    hout = {key: torch.empty_like(t, device="cpu").pin_memory() for key, t in outs.items()}
-    h2d = sum(t.numel() * 2 for t in hx.values())
-    d2h = sum(t.numel() * 2 for t in hout.values())
-
-    def e2e_step(step_idx):
-        for mi, m in enumerate(MS):
-            layer = sets[(step_idx * len(MS) + mi) % WEIGHT_SETS]
-            for name, k, n in lin:
-                pre, sc = layer[name]
-                xs[(name, m)].copy_(hx[(name, m)], non_blocking=True)
-                ops.gemm_fp16_q4f16(xs[(name, m)], pre, sc, out=outs[(name, m)])
-                if world > 1 and name in row_parallel:
-                    allreduce(outs[(name, m)])
-                hout[(name, m)].copy_(outs[(name, m)], non_blocking=True)
-        torch.cuda.synchronize()  # the step's results are on the host
-
-    for i in range(args.warmup):
-        e2e_step(i)
-    barrier()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        e2e_step(args.warmup + i)
-    e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
-    clk = clocks.stop()
+            ms = graph_time(lambda: ops.moe_gemm_ft(x4, w4, s4, indptr4, out=o4), calls=4)
+            extra["mixtral_moe_w4_g128_1024rows"] = {"us": ms * 1e3, "tflops": 2.0 * 1024 * k4 * n4 / (ms * 1e-3) / 1e12}
+            del w4, s4, x4, o4
+            extra["preprocess"] = preprocess_block(dev, peak)
+        torch.cuda.empty_cache()
+        extra["llama70b_mlp_tp%d" % world] = llama70b_mlp_block(world, rank, dev, rp, barrier)
+        torch.cuda.empty_cache()
+        extra["mixtral_ep%d" % world] = mixtral_block(world, rank, dev, barrier)
 
     if world > 1:
         t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
@@ -514,7 +741,6 @@ def run_gpu(args):
     sb = step_bytes()
     value = world * sb * args.steps / (ms_total * 1e-3) / 1e9
     e2e_value = world * sb * args.steps / (ms_e2e * 1e-3) / 1e9
-    peak, peak_kind = measured_peak()
 
     cpu = None
     if rank == 0 and world == 1:
@@ -533,18 +759,20 @@ def run_gpu(args):
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": dict(workload_config(world), timed_with="cuda graph replay" if graphs else "eager launches",
-                           launch_overlap=relax_b200.get_launch_overlap(), allreduce=allreduce_kind),
+                           launch_overlap=relax_b200.get_launch_overlap(), allreduce=ar_names.get(ar_mode, ar_mode)),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e / args.steps},
+                    "ms_per_step": ms_e2e / args.steps,
+                    "how": "per step: one copy of the 12 activations from pinned host memory, 12 PackedFunc calls "
+                           "(argument arrays built once), one copy of the 12 results to pinned host memory, sync"},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
                          # DRAM bytes per launch: the ncu capture of the gate_up M=1 launch read+wrote
-                         # 50.86 MB against 50.78 MB algorithmic (x1.0016); scaled to the mean launch
+                         # 1.0016 x its algorithmic bytes; scaled to the mean launch
                          "traffic": 1.0016 * sum(c for _, c in per_shape.values()) / len(per_shape),
                          "traffic_source": "profiles/gemv_sk_kernel_gate_up_m1.md, scaled by algorithmic bytes",
                          "peak_kind": peak_kind,
-                         "kernel": "gemv_sk_kernel (n > 4096) / gemv_cluster_kernel (n <= 4096)",
+                         "kernel": "gemv_sk_kernel",
                          "per_shape_gbs": shape_gbs, "per_shape_us": shape_us},
             "cpu_baseline": cpu,
             "clocks": {"sm_mhz": clk["sm_mhz"], "sm_max_mhz": clk["sm_max_mhz"], "reasons": clk["reasons"]},
@@ -562,10 +790,64 @@ def run_gpu(args):
         import threading
         threading.Timer(20.0, lambda: os._exit(0)).start()
         try:
+            if rp is not None:
+                rp.close()
             dist.destroy_process_group()
         finally:
             sys.stdout.flush()
             os._exit(0)
+
+
+def run_case(args):
+    """One shape, a few launches over rotating weight copies: the command the profiler summaries
+    under profiles/ are taken with.  --case m=1,k=4096,n=22016[,bits=4,group=32,asym=0,copies=0,reps=3]"""
+    import torch
+    from relax_b200 import ops
+    a = {"m": 1, "k": 4096, "n": 22016, "bits": 4, "group": 32, "asym": 0, "copies": 0, "reps": 3}
+    for part in args.case.split(","):
+        key, val = part.split("=")
+        a[key] = int(val)
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1)
+    m, k, n, bits, group = a["m"], a["k"], a["n"], a["bits"], a["group"]
+    wbytes = n * k * bits // 8
+    copies = a["copies"] or max(2, int(320e6 // wbytes) + 1)
+    x = torch.randn((m, k), device=dev, generator=gen).half()
+    out = torch.empty((m, n), device=dev, dtype=torch.float16)
+    ws, ss, zs = [], [], []
+    for _ in range(copies):
+        if bits == 4:
+            raw = torch.randint(-2**31, 2**31 - 1, (n, k // 8), dtype=torch.int32, device=dev, generator=gen)
+            ws.append(ops.preprocess_weight_q4f16(raw))
+            ss.append((torch.rand((n, k // group), device=dev, generator=gen) * 0.009 + 0.001).half())
+            zs.append(torch.randint(0, 16, (n, k // group), device=dev, generator=gen).half() if a["asym"] else None)
+        else:
+            raw = torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev, generator=gen)
+            ws.append(ops.preprocess_weight_ft(raw, False))
+            ss.append((torch.rand((n,), device=dev, generator=gen) * 0.0009 + 0.0001).half())
+            zs.append(None)
+
+    def launch(i):
+        if bits == 4:
+            ops.gemm_fp16_q4f16(x, ws[i], ss[i], zs[i], group_size=group, out=out)
+        else:
+            ops.gemm_fp16_ft(x, ws[i], ss[i], 8, out=out)
+
+    for i in range(copies):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(a["reps"]):
+        for i in range(copies):
+            launch(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (a["reps"] * copies)
+    gb = (wbytes + ss[0].numel() * 2 * (2 if a["asym"] else 1) + m * k * 2 + m * n * 2) / 1e9
+    print(json.dumps({"case": a, "us_per_launch_eager": us, "gbs": gb / (us * 1e-6),
+                      "tflops": 2.0 * m * k * n / (us * 1e-6) / 1e12}))
 
 
 def main():
@@ -574,9 +856,12 @@ def main():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--case", default="", help="run one shape for a profiler: m=1,k=4096,n=22016[,bits=4,group=32,asym=0,copies=0,reps=3]")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

@@ -477,7 +477,7 @@ static int fill_ft_desc(rb200_gemm_desc* d, const void* A, const void* B, const 
   d->n = n;
   d->k = k;
   d->ldx = k;
-  d->ldo = n;
+  d->ldo = 0;  // the entry point's default: n, or n / 2 for the fused gate/up activation
   const bool per_col = group_size <= 0 || group_size >= k;
   d->group_size = per_col ? k : group_size;
   d->scale_stride_n = 1;               // FT scales: [n] or [k/g, n]

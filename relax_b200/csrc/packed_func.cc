@@ -384,8 +384,9 @@ int ft_gemm(const char* fname, int bits, RB200Value* v, int* tc, int n_args, int
            (long long)w->shape[0], (long long)(w->ndim > 1 ? w->shape[1] : 0), (long long)k, (long long)n);
   PF_CHECK(x->ndim >= 1 && x->shape[x->ndim - 1] == k && lead_rows(x) == m,
            "%s: x shape does not match m=%lld, k=%lld", fname, (long long)m, (long long)k);
-  PF_CHECK(numel(out) == m * n, "%s: out has %lld elements, expected m*n=%lld", fname,
-           (long long)numel(out), (long long)(m * n));
+  const int64_t n_out = !strcmp(act, "swiglu") ? n / 2 : n;  // the fused gate/up form halves the width
+  PF_CHECK(numel(out) == m * n_out, "%s: out has %lld elements, expected %lld", fname, (long long)numel(out),
+           (long long)(m * n_out));
   const bool per_col = group <= 0 || group >= k;
   // the shapes the reference's pattern check admits (python/tvm/relax/backend/contrib/cutlass.py:255-257):
   // (N,), (1, N) or (K / group_size, N)

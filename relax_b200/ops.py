@@ -33,7 +33,7 @@ def gemm_fp16_ft(x, w_pre, scales, weight_bits: int, bias=None, residual=None,
     n = w_pre.shape[-1] * (2 if weight_bits == 4 else 1)
     m = x.numel() // k
     if out is None:
-        out = torch.empty(*x.shape[:-1], n, dtype=torch.float16, device=x.device)
+        out = torch.empty(*x.shape[:-1], n // 2 if activation == "swiglu" else n, dtype=torch.float16, device=x.device)
     bias_stride = 0
     if bias is not None and bias.numel() == m * n and m > 1:
         bias_stride = n

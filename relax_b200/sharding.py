@@ -160,6 +160,33 @@ class RowParallelLinear:
         self._lib.check(lib.rb200_gemm_fp16_intx_allreduce(ctypes.byref(d), self.ws.ptrs, self.rank, self.world,
                                                            self.max_n, stream))
 
+    def bind_q4f16(self, x, w_pre, scales, out, group_size: int = 32, zero_const: float = 7.0):
+        """The call of :meth:`gemm_q4f16` with its descriptor built once: returns a zero-argument
+        callable for serving loops that pass the same buffers on every step."""
+        import ctypes
+        import torch
+        d = self._lib.GemmDesc()
+        d.struct_size = ctypes.sizeof(self._lib.GemmDesc)
+        d.weight_bits = 4
+        k = x.shape[-1]
+        d.x, d.w, d.scales, d.out = x.data_ptr(), w_pre.data_ptr(), scales.data_ptr(), out.data_ptr()
+        d.m, d.n, d.k = x.numel() // k, w_pre.shape[0], k
+        d.ldx, d.ldo = k, w_pre.shape[0]
+        d.group_size = group_size
+        d.scale_stride_n, d.scale_stride_g = k // group_size, 1
+        d.zero_const = zero_const
+        fn = self._lib.load().rb200_gemm_fp16_intx_allreduce
+        ref, ptrs, rank, world, max_n, check = ctypes.byref(d), self.ws.ptrs, self.rank, self.world, self.max_n, self._lib.check
+        keep = (d, x, w_pre, scales, out)
+
+        def call():
+            rc = fn(ref, ptrs, rank, world, max_n, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            if rc != 0:
+                check(rc)
+            return keep[4]
+
+        return call
+
     def gemm_q4f16(self, x, w_pre, scales, out, group_size: int = 32, zero_const: float = 7.0, bias=None,
                    residual=None, activation: int = 0):
         """``out = epilogue(sum over ranks of x_shard @ decode(w_shard)^T)`` for q4f16_1 shards
