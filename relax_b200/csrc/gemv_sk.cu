@@ -59,7 +59,7 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   if (stages > sk::kConsumerWarps) stages = sk::kConsumerWarps;  // one consumer warp starts each stage
   if (stages < 2) stages = 2;
   p.stages = stages;
-  l.smem_bytes = 1024 + (size_t)stages * sb + (size_t)stages * 2 * sizeof(uint64_t);  // 1 KB: alignment slack
+  l.smem_bytes = 1024 + (size_t)stages * sb + (size_t)(stages + 1) * 2 * sizeof(uint64_t);  // 1 KB: alignment slack
   long long grid = (long long)sm_count * ctas_per_sm;
   if (grid > p.total_iters) grid = p.total_iters;
   l.grid = (int)grid;

@@ -76,30 +76,30 @@ struct StageLayout {
 
 // Row-parallel epilogue fused with the sum over ranks (world > 1).  Every rank owns a workspace
 // its peers can address:
-//   [ header 256 B: u32 calls, u32 warps_done | flags u32 [kArMaxRanks][max_blocks] |
-//     data fp32 [2 regions][kArMaxRanks][max_blocks][kArSlotFloats] ]
+//   [ header 256 B: u32 calls, u32 ctas_done |
+//     data [2 regions][kArMaxRanks][max_blocks][kArSlotWords] x 8 bytes ]
 // A warp that has the final fp32 fragment of a 16-row block writes it into slot [rank][block] of
-// EVERY rank's workspace (its own included), fences, and stores the call number into flag
-// [rank][block] of every peer.  At the very end of the kernel the same warp waits - bounded -
-// until its own flags [p][block] show the call number for every peer p, adds the slots in rank
-// order (so every rank forms the same bits), applies the epilogue, rounds once and stores.
+// EVERY rank's workspace (its own included) as 8-byte words {value, call number}: an aligned
+// 8-byte store arrives whole, so the word is its own flag and no fence is needed anywhere (a
+// system-scope fence costs several microseconds, two of them per exchange more than the matmul).
+// At the very end of the kernel the same warp reads its own copy of every rank's slot, polling -
+// bounded - each word until it carries the call number, adds the values in rank order (so every
+// rank forms the same bits), applies the epilogue, rounds once and stores.
 // The call number is kept on the device (header), which makes the launch graph-replayable; the
 // two data regions alternate with its parity, because a peer may still be reading call i when
 // this rank is already publishing call i + 1 (it cannot reach call i + 2: that needs the peer's
-// flags of call i + 1, which the peer writes after it finished call i).
+// words of call i + 1, which the peer writes after it finished call i), and a word left from
+// call i - 2 never carries the number of call i.
 constexpr int kArMaxRanks = 8;
-constexpr int kArSlotFloats = 4 * 128;  // four m-tiles of one 16-row block
+constexpr int kArSlotWords = 4 * 128;  // four m-tiles of one 16-row block, one 8-byte word per value
 constexpr size_t kArHeaderBytes = 256;
 struct ArCtx {
   uint8_t* ws[kArMaxRanks];  // ws[r]: rank r's workspace as this GPU addresses it
   int rank, world;           // world <= 1: no exchange
   unsigned max_blocks;       // 16-row blocks a region has room for
 };
-__host__ __device__ __forceinline__ size_t ar_flags_bytes(unsigned max_blocks) {
-  return (((size_t)kArMaxRanks * max_blocks * 4) + 255) / 256 * 256;
-}
 __host__ __device__ __forceinline__ size_t ar_workspace_bytes(unsigned max_blocks) {
-  return kArHeaderBytes + ar_flags_bytes(max_blocks) + (size_t)2 * kArMaxRanks * max_blocks * kArSlotFloats * 4;
+  return kArHeaderBytes + (size_t)2 * kArMaxRanks * max_blocks * kArSlotWords * 8;
 }
 
 struct Params {
@@ -209,17 +209,12 @@ struct ScalePlan {
   static constexpr int kCount = kChunk / kSpan;
 };
 
-__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_volatile_v2(uint2* p, uint32_t x, uint32_t y) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_volatile_f32(const float* p) {
-  float v;
-  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_volatile_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ unsigned atom_inc_acq_rel_shared(unsigned* p) {
@@ -258,6 +253,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(&full_bar[s], 1);  // the issuing lane's expect_tx arrival; the copies complete the bytes
       drained[s] = 0u;
     }
+    drained[stages] = 0u;  // warps of this CTA through with the all-reduce epilogue
     mbar_fence_init();
   }
   fence_proxy_async();
@@ -406,64 +402,62 @@ __global__ void __launch_bounds__(kThreads, 2)
   // ---- all-reduce side of the epilogue (see ArCtx)
   const bool ar_on = AR && pp.ar.world > 1;
   unsigned ar_call = 0;
-  auto ar_slot = [&](int r, unsigned call, int src, int blk) -> float* {
-    return reinterpret_cast<float*>(pp.ar.ws[r] + kArHeaderBytes + ar_flags_bytes(pp.ar.max_blocks)) +
-           ((size_t)((call & 1u) * kArMaxRanks + (unsigned)src) * pp.ar.max_blocks + (unsigned)blk) * kArSlotFloats;
-  };
-  auto ar_flag = [&](int r, int src, int blk) -> unsigned* {
-    return reinterpret_cast<unsigned*>(pp.ar.ws[r] + kArHeaderBytes) + (size_t)src * pp.ar.max_blocks + blk;
+  auto ar_slot = [&](int r, unsigned call, int src, int blk) -> uint2* {
+    return reinterpret_cast<uint2*>(pp.ar.ws[r] + kArHeaderBytes) +
+           ((size_t)((call & 1u) * kArMaxRanks + (unsigned)src) * pp.ar.max_blocks + (unsigned)blk) * kArSlotWords;
   };
   // this rank's part of a block is final: hand it to every rank
   auto ar_publish = [&](const float (&v)[MT][4], int tile_i) {
     const int blk = tile_i * kConsumerWarps + warp;
     if (blk >= n_blocks) return;
     for (int r = 0; r < pp.ar.world; ++r) {
-      float* dst = ar_slot(r, ar_call, pp.ar.rank, blk) + lane;
+      uint2* dst = ar_slot(r, ar_call, pp.ar.rank, blk) + lane;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) dst[(mt * 4 + c) * 32] = v[mt][c];
-    }
-    __syncwarp();
-    if (lane < pp.ar.world && lane != pp.ar.rank) {
-      __threadfence_system();
-      st_release_sys_u32(ar_flag(lane, pp.ar.rank, blk), ar_call);
+        for (int c = 0; c < 4; ++c) st_volatile_v2(dst + (mt * 4 + c) * 32, __float_as_uint(v[mt][c]), ar_call);
     }
   };
-  // all ranks' parts of a block: wait, add in rank order, finish
+  // all ranks' parts of a block: wait for the words, add in rank order, finish
   auto ar_finish = [&](int tile_i, unsigned long long limit_ns) -> bool {
     const int blk = tile_i * kConsumerWarps + warp;
     if (blk >= n_blocks) return true;
-    bool arrived = true;
-    if (lane < pp.ar.world && lane != pp.ar.rank) {
-      const unsigned* f = ar_flag(pp.ar.rank, lane, blk);
-      if ((int)(ld_acquire_sys_u32(f) - ar_call) < 0) {
-        unsigned long long t0;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        while ((int)(ld_acquire_sys_u32(f) - ar_call) < 0) {  // flags only grow: a peer may be a call ahead
-          unsigned long long t1;
-          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-          if (t1 - t0 > limit_ns) {
-            if (p.status) atomicExch(p.status, kStatusWaitTimeout);
-            arrived = false;
-            break;
-          }
-        }
-      }
-    }
-    if (!__all_sync(0xffffffffu, arrived)) return false;
     float sum[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int c = 0; c < 4; ++c) sum[mt][c] = 0.0f;
-    for (int r = 0; r < pp.ar.world; ++r) {
-      const float* src = ar_slot(pp.ar.rank, ar_call, r, blk) + lane;
+    bool arrived = true;
+    for (int r = 0; r < pp.ar.world && arrived; ++r) {
+      const uint2* src = ar_slot(pp.ar.rank, ar_call, r, blk) + lane;
+      uint2 w[MT][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) sum[mt][c] += ld_volatile_f32(src + (mt * 4 + c) * 32);
+        for (int c = 0; c < 4; ++c) w[mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (w[mt][c].y != ar_call) {  // not there yet: poll this word
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            do {
+              w[mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
+              unsigned long long t1;
+              asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+              if (t1 - t0 > limit_ns) {
+                if (p.status) atomicExch(p.status, kStatusWaitTimeout);
+                arrived = false;
+                break;
+              }
+            } while (w[mt][c].y != ar_call);
+          }
+          sum[mt][c] += __uint_as_float(w[mt][c].x);
+        }
+      arrived = __all_sync(0xffffffffu, arrived);
     }
+    if (!arrived) return false;
     store_tile(sum, tile_i);
     return true;
   };
@@ -745,17 +739,15 @@ __global__ void __launch_bounds__(kThreads, 2)
         if (pc.kind == kWhole) fine = ar_finish(pc.tile, limit_ns);
       if (fine && head_published) ar_finish(head_tile, limit_ns);
     }
-    // the call is over when every warp of the grid is through: the last one advances the
+    // the call is over when every warp of the grid is through: the last CTA advances the
     // device-side call number (read by the next launch after its dependency wait)
     griddep_wait();
     if (ar_call == 0) ar_call = *reinterpret_cast<volatile unsigned*>(pp.ar.ws[pp.ar.rank]) + 1u;
     __syncwarp();
-    if (lane == 0) {
+    if (lane == 0 && atom_inc_acq_rel_shared(&drained[stages]) == kConsumerWarps - 1) {
       unsigned* hdr = reinterpret_cast<unsigned*>(pp.ar.ws[pp.ar.rank]);
-      __threadfence();
-      if (atomicAdd(hdr + 1, 1u) == grid * kConsumerWarps - 1u) {
+      if (atomicAdd(hdr + 1, 1u) == grid - 1u) {
         hdr[1] = 0u;
-        __threadfence();
         *reinterpret_cast<volatile unsigned*>(hdr) = ar_call;
       }
     }

@@ -123,6 +123,96 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
   }
 }
 
+// FT source ([K, N] bytes for int8, [K, N/2] bytes for int4, both contiguous along n) without the
+// gate/up interleave: the fragment layout gathers along k, the source is contiguous along n, so
+// a byte gather straight from global memory wastes 15 of every 16 bytes of each sector it
+// touches.  Here a CTA stages one panel - the kFrag k-rows of one fragment k-block x 512 output
+// columns (16 KB) - in shared memory with 16-byte (int8) / 8-byte (int4) loads that are coalesced
+// along n, and every lane then gathers its 16-byte unit from shared memory; the 32 units of a
+// fragment tile leave as one 512-byte segment.  The 16-byte chunks of panel row k are stored at
+// chunk ^ (row quarter), so that the four lane groups of a warp, which read rows a quarter of
+// the block apart, hit different banks.
+template <int BITS>
+__global__ void __launch_bounds__(256) repack_ft_panel_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                              int64_t K, int64_t N, int64_t panels_per_kb,
+                                                              int64_t total_panels) {
+  constexpr int kFrag = BITS == 4 ? 64 : 32;         // k rows of a panel
+  constexpr int kRowBytes = BITS == 4 ? 256 : 512;   // 512 output columns
+  constexpr int kChunks = kRowBytes / 16;
+  constexpr int kQuarter = kFrag / 4;                // k rows per lane group t
+  __shared__ __align__(16) uint8_t panel[kFrag * kRowBytes];
+  const int64_t KB = K / kFrag, NB = N / 16;
+  const int64_t row_bytes = N * BITS / 8;
+  const int64_t expert_bytes = K * row_bytes;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  for (int64_t pi = blockIdx.x; pi < total_panels; pi += gridDim.x) {
+    const int64_t e = pi / (KB * panels_per_kb);
+    const int64_t rem = pi % (KB * panels_per_kb);
+    const int64_t kb = rem / panels_per_kb, pn = rem % panels_per_kb;
+    const int64_t byte0 = pn * kRowBytes;                       // first byte of the panel inside a source row
+    const int64_t valid = min((int64_t)kRowBytes, row_bytes - byte0);
+    const uint8_t* s = src + e * expert_bytes + kb * kFrag * row_bytes + byte0;
+    __syncthreads();  // the previous panel has been read
+    if (BITS == 8) {
+      for (int i = tid; i < kFrag * kChunks; i += 256) {
+        const int r = i / kChunks, c = i % kChunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (c * 16 < valid) v = *reinterpret_cast<const uint4*>(s + r * row_bytes + c * 16);
+        *reinterpret_cast<uint4*>(panel + r * kRowBytes + ((c ^ ((r / kQuarter) & 3)) << 4)) = v;
+      }
+    } else {
+      for (int i = tid; i < kFrag * kChunks * 2; i += 256) {
+        const int r = i / (kChunks * 2), h = i % (kChunks * 2);  // 8-byte halves: rows are only 8-byte aligned
+        uint2 v = make_uint2(0u, 0u);
+        if (h * 8 < valid) v = *reinterpret_cast<const uint2*>(s + r * row_bytes + h * 8);
+        *reinterpret_cast<uint2*>(panel + r * kRowBytes + (((h >> 1) ^ ((r / kQuarter) & 3)) << 4) + (h & 1) * 8) = v;
+      }
+    }
+    __syncthreads();
+    // 32 fragment tiles (16 output rows each) per panel, four per warp
+    for (int bi = warp; bi < 32; bi += 8) {
+      const int64_t nb = pn * 32 + bi;
+      if (nb >= NB) break;
+      uint32_t words[4];
+      if (BITS == 8) {
+        // unit: rows g, g + 8; k = 8 t .. 8 t + 7; word 2 j + r8 = row g + 8 r8, k 4 j .. 4 j + 3
+        const uint8_t* base = panel + ((bi ^ t) << 4) + g;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int r8 = 0; r8 < 2; ++r8) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)
+              w |= ((uint32_t)base[(t * 8 + 4 * j + c4) * kRowBytes + 8 * r8] ^ 0x80u) << (8 * c4);
+            words[2 * j + r8] = w;
+          }
+      } else {
+        // unit: rows g, g + 8; k = 16 t .. 16 t + 15; word j covers k4 = 4 j .. 4 j + 3 with nibble
+        // slots p0 (g,k4) p4 (g,k4+1) p2 (g,k4+2) p6 (g,k4+3), p1 p5 p3 p7 the same for g + 8
+        const uint8_t* base = panel + (((bi >> 1) ^ t) << 4) + (bi & 1) * 8 + (g >> 1);
+        const int sh = (g & 1) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t w = 0;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint8_t* rowp = base + (t * 16 + 4 * j + kk) * kRowBytes;
+            const uint32_t lo = (((uint32_t)rowp[0] >> sh) & 15u) ^ 8u;   // row g
+            const uint32_t hi = (((uint32_t)rowp[4] >> sh) & 15u) ^ 8u;   // row g + 8
+            const int slot = kk == 0 ? 0 : (kk == 1 ? 4 : (kk == 2 ? 2 : 6));
+            w |= (lo << (4 * slot)) | (hi << (4 * (slot + 1)));
+          }
+          words[j] = w;
+        }
+      }
+      reinterpret_cast<uint4*>(dst + e * expert_bytes + frag_tile_offset(nb, kb, NB, KB))[frag_unit_pos(lane)] =
+          make_uint4(words[0], words[1], words[2], words[3]);
+    }
+  }
+}
+
 }  // namespace
 
 // dst[o][j][i] = src[o][gate_up_source_row(j)][i] over fp16 elements: the row permutation of the
@@ -148,6 +238,17 @@ int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, in
   if (blocks == 0) return 0;
   const uint8_t* s = static_cast<const uint8_t*>(src);
   uint8_t* d = static_cast<uint8_t*>(dst);
+  if (layout == 0 && !interleave && (reinterpret_cast<uintptr_t>(src) & (bits == 8 ? 15u : 7u)) == 0) {
+    // FT source: staged through shared memory, coalesced both ways
+    const int64_t panels_per_kb = (n + 511) / 512;
+    const int64_t total_panels = experts * (k / (bits == 4 ? 64 : 32)) * panels_per_kb;
+    int64_t grid = total_panels;
+    if (grid > (int64_t)sm_count_current() * 32) grid = (int64_t)sm_count_current() * 32;
+    if (bits == 4) repack_ft_panel_kernel<4><<<(int)grid, 256, 0, stream>>>(s, d, k, n, panels_per_kb, total_panels);
+    else repack_ft_panel_kernel<8><<<(int)grid, 256, 0, stream>>>(s, d, k, n, panels_per_kb, total_panels);
+    RB200_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (bits == 4 && layout == 0)
     repack_kernel<4, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
   else if (bits == 4 && layout == 1)

@@ -2,9 +2,13 @@
 //
 //   out^T tile [128 weight rows x up to 256 batch rows] = W_tile [128 x K] * x_tile^T [K x 256]
 //
-// tcgen05.mma (kind::f16, M = 128, K = 16) costs about 172 clocks per instruction on B200
-// whatever its N, so the batch is the instruction's N and is made as wide as it goes (256): one
-// instruction then does 128 x 256 x 16 MACs.  The dequantised weights are the A operand and never
+// Measured on B200: one tcgen05.mma (kind::f16, M = 128, K = 16, A from tensor memory) occupies
+// the tensor pipe for 108 clocks for any N up to 192 and for 136 clocks at N = 256, so the batch
+// is the instruction's N and is made as wide as it goes (256): one instruction then does
+// 128 x 256 x 16 MACs.  (A variant with N = 192, two accumulators - epilogue overlapped with the
+// next tile's main loop - and four decode groups was measured slower, 874 against 1065 TFLOP/s:
+// every CTA streams the whole x tile from L2 for each 128-row weight tile, 148 CTAs together
+// 7-8 TB/s, and that traffic, not the tensor pipe, bounds the main loop.)  The dequantised weights are the A operand and never
 // touch shared memory: decode warps write them straight into tensor memory (tcgen05.st), the MMA
 // reads A from TMEM and B (= x) from a 128B-swizzled K-major tile in shared memory, the fp32
 // accumulator sits in 256 TMEM columns.
@@ -216,7 +220,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr int kFragK = BITS == 8 ? 32 : 64;
   extern __shared__ uint8_t smem_raw[];
   const GemvParams& p = pp.g;
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // 1 KB alignment as an offset from the array (a pointer rebuilt from an integer would turn
+  // every shared-memory access of the decode warps into a generic one)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int nb = pp.nb;
   const int x_stages = pp.x_stages;
   const int x_stage_bytes = nb * 128;

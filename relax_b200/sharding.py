@@ -93,6 +93,34 @@ def allreduce_sum_(t, group=None):
     return t
 
 
+class RankMonitor:
+    """Host-side membership for the ranks of one job: a rank that stops taking part (shutdown,
+    preemption, an exception in its serving loop) says so through a key-value store before it
+    goes, and the others look before their next launch.  A kernel that waits for a peer which is
+    gone would sit out its bounded wait (``rb200_set_wait_limit_ms``) and report through the status
+    word; with this check the survivors never launch it.  The reference has no counterpart: its
+    collectives abort the process on any NCCL error (src/runtime/disco/nccl/nccl_context.h:50-56)
+    and its customized all-reduce spins without a bound
+    (3rdparty/tensorrt_llm/custom_allreduce_kernels.cu:94-113).
+
+    ``store`` is any ``torch.distributed`` store (``TCPStore``, ``FileStore``, the default store of
+    an initialised process group)."""
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "rb200/left/"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def leave(self, reason: str = "") -> None:
+        """Call between steps, with none of this rank's kernels or collectives in flight."""
+        self.store.set(self.prefix + str(self.rank), reason or "left")
+
+    def departed(self):
+        """Ranks that have announced their departure (cheap: one store query per peer)."""
+        return [r for r in range(self.world) if r != self.rank and self.store.check([self.prefix + str(r)])]
+
+    def all_present(self) -> bool:
+        return not self.departed()
+
+
 class PeerWorkspace:
     """A zero-filled device buffer of this rank that every rank of the group can address: allocated
     with ``rb200_peer_alloc``, its CUDA IPC handle exchanged over ``torch.distributed`` (host bytes

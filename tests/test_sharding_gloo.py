@@ -68,6 +68,58 @@ def test_world_size_2_shards_reassemble():
     assert ret.get(0) is True and ret.get(1) is True
 
 
+def _leaving_worker(rank, world, port, store_port, ret):
+    """Step 1 with both ranks; rank 1 then leaves between steps.  Rank 0 must learn of it on the
+    host before its next launch, and a collective it started anyway must end with an error, not
+    hang."""
+    import datetime
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    from relax_b200 import sharding
+    store = dist.TCPStore("127.0.0.1", store_port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=30))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    mon = sharding.RankMonitor(store, rank, world)
+    t = torch.ones(8) * (rank + 1)
+    assert mon.all_present()
+    sharding.allreduce_sum_(t)  # step 1: everyone is there
+    ok = bool(torch.all(t == 3))
+    if rank == 1:
+        mon.leave("shutting down")  # between steps, nothing in flight
+        ret[rank] = ok
+        store.wait(["rb200/test/seen"])  # keep the store's client alive until rank 0 has looked
+        dist.destroy_process_group()
+        return
+    deadline = time.time() + 20
+    while mon.all_present() and time.time() < deadline:
+        time.sleep(0.05)
+    ok &= mon.departed() == [1]  # learnt on the host: the survivor launches nothing for step 2
+    store.set("rb200/test/seen", "1")
+    # what would have happened without the check: the collective fails within the group's timeout
+    time.sleep(0.5)
+    t0 = time.time()
+    failed = False
+    try:
+        dist.all_reduce(torch.ones(8))
+    except Exception:
+        failed = True
+    ok &= failed and (time.time() - t0) < 15
+    ret[rank] = ok
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+def test_a_rank_that_leaves_between_steps_is_noticed_on_the_host():
+    port = 30500 + (os.getpid() % 1000)
+    mgr = mp.get_context("spawn").Manager()
+    ret = mgr.dict()
+    mp.spawn(_leaving_worker, args=(2, port, port + 1500, ret), nprocs=2, join=True)
+    assert ret.get(0) is True and ret.get(1) is True, dict(ret)
+
+
 def test_shard_validation():
     sys.path.insert(0, ROOT)
     from relax_b200 import sharding
