@@ -99,10 +99,30 @@ RB200_API int rb200_preprocess_weight(const void* src, void* dst, int64_t num_ex
  * [groups, n/8], nibble j of word (g, n/8) = column 8*(n/8) + j.  Writes fp16 [groups, n] holding
  * f16(zq) + f16(1) - the value that decode subtracts - ready to be passed as the `zeros` tensor
  * of rb200_gemm_fp16_intx with scale_stride_n = 1, scale_stride_g = n.  The matmul entries take
- * groups in order along k (g_idx[k] = k / group_size); an arbitrary g_idx permutation is not
- * supported.
+ * groups in order along k (g_idx[k] = k / group_size); for an arbitrary g_idx see
+ * rb200_gptq_act_order below.
  */
 RB200_API int rb200_unpack_zeros_autogptq(const void* zq, void* zeros_out, int64_t groups, int64_t n, void* stream);
+
+/*
+ * Act-order AutoGPTQ weights: the reference decode reads scale and zero of element k through
+ * g_idx[k] (tests/python/dlight/test_gpu_gemv.py:646-648, `lv12[v_i]`).  The matmul kernels want
+ * groups contiguous along k, so the reduction axis is permuted once at load time:
+ *   rb200_gptq_act_order                  g_idx int32 [k] (device) -> perm int32 [k] (device): the k rows listed
+ *                                         group by group, original order inside a group.  Every
+ *                                         group must have exactly k / groups rows (error otherwise).
+ *                                         Set-up routine: synchronises the stream, allocates 4 bytes.
+ *   rb200_preprocess_weight_autogptq_perm repack of qweight uint32 [k/8, n] with row perm[j] of the
+ *                                         source at position j of the reduction axis
+ *   rb200_gather_columns                  out[m, j] = x[m, perm[j]] (fp16), run before each matmul
+ * With these, gemm(gather(x), repacked weight, scales, zeros) sums the same products as the
+ * reference's x @ decode(W, g_idx), in a different order.
+ */
+RB200_API int rb200_gptq_act_order(const int32_t* g_idx, int64_t k, int64_t groups, int32_t* perm_out, void* stream);
+RB200_API int rb200_preprocess_weight_autogptq_perm(const void* qweight, void* dst, int64_t k, int64_t n,
+                                                    const int32_t* perm, void* stream);
+RB200_API int rb200_gather_columns(const void* x, const int32_t* perm, void* out, int64_t m, int64_t k,
+                                   int64_t ldx, int64_t ldo, void* stream);
 
 /* ------------------------------------------------------------------ dequantize-matmul */
 

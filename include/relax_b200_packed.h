@@ -111,7 +111,11 @@ RB200_API int RB200FuncListGlobalNames(int* out_size, const char*** out_array);
  *  "relax_b200.preprocess_weight_gate_up"(packed_weight, layout:int, is_int4:int, out)   repack with the
  *      gate/up row interleave; "relax_b200.interleave_gate_up"(f16 tensor, n_axis:int, out) permutes
  *      scales / zeros alike; activation "swiglu" of the matmul entries then writes silu(gate) * up.
- *  "relax_b200.preprocess_weight_autogptq"(qweight u32 [K/8, N], out)   AutoGPTQ source layout
+ *  "relax_b200.preprocess_weight_autogptq"(qweight u32 [K/8, N], out[, perm i32 [K]])   AutoGPTQ source
+ *      layout; with perm, source row perm[j] lands at position j of the reduction axis (act-order)
+ *  "relax_b200.gptq_act_order"(g_idx i32 [K], groups:int, perm_out i32 [K])   the k rows group by group
+ *      (tests/python/dlight/test_gpu_gemv.py:646-648 indexes scales and zeros through g_idx)
+ *  "relax_b200.gather_columns"(x f16 [.., K], perm i32 [K], out f16 like x)   out[.., j] = x[.., perm[j]]
  *  "relax_b200.unpack_zeros_autogptq"(qzeros u32 [G, N/8], out f16 [G, N])   f16(zq) + 1
  *  "relax_b200.gemm_fp16_autogptq"(x, w_pre, scales f16 [G, N], zeros f16 [G, N], bias|null, out)
  *      the decode + matmul + add of tests/python/dlight/test_gpu_gemv.py:639-661, fp32 accumulation.

@@ -94,6 +94,9 @@ SIGNATURES = {
     "rb200_interleave_gate_up": (_I, [_V, _V, _I64, _I64, _I64, _V]),
     "rb200_encode_ft": (_I, [_V, _V, _V, _I64, _I64, _I, _I64, _V]),
     "rb200_unpack_zeros_autogptq": (_I, [_V, _V, _I64, _I64, _V]),
+    "rb200_gptq_act_order": (_I, [_V, _I64, _I64, _V, _V]),
+    "rb200_preprocess_weight_autogptq_perm": (_I, [_V, _V, _I64, _I64, _V, _V]),
+    "rb200_gather_columns": (_I, [_V, _V, _V, _I64, _I64, _I64, _I64, _V]),
     "rb200_gemm_fp16_intx": (_I, [ctypes.POINTER(GemmDesc), _V]),
     "rb200_gemm_fp16_intx_noalloc": (_I, [ctypes.POINTER(GemmDesc), _V]),
     "rb200_gemm_allreduce_workspace_bytes": (ctypes.c_size_t, [_I64]),

@@ -291,8 +291,47 @@ int rb200_preprocess_weight(const void* src, void* dst, int64_t num_experts, int
   RB200_CHECK(aligned16(dst), "dst must be 16-byte aligned");
   RB200_CHECK(base_layout != RB200_LAYOUT_Q4_NK || (reinterpret_cast<uintptr_t>(src) & 7u) == 0,
               "a q4f16_1 source must be 8-byte aligned");
-  return preprocess_launch(src, dst, num_experts, k, n, bits, src_layout,
+  return preprocess_launch(src, dst, num_experts, k, n, bits, src_layout, nullptr,
                            static_cast<cudaStream_t>(stream));
+}
+
+int rb200_gptq_act_order(const int32_t* g_idx, int64_t k, int64_t groups, int32_t* perm_out, void* stream) {
+  RB200_CHECK(g_idx && perm_out, "g_idx and perm_out must be non-NULL");
+  RB200_CHECK(k > 0 && groups > 0 && k % groups == 0 && k < (1ll << 30) && groups <= 8192,
+              "need groups dividing k, at most 8192 groups (k=%lld, groups=%lld)", (long long)k, (long long)groups);
+  // set-up time routine (once per weight): a status word of its own, read back before returning
+  int* d_status = nullptr;
+  RB200_CUDA(cudaMalloc(&d_status, sizeof(int)));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = gptq_act_order_launch(g_idx, k, groups, perm_out, d_status, st);
+  int h_status = -1;
+  cudaError_t e = cudaSuccess;
+  if (rc == 0) e = cudaMemcpyAsync(&h_status, d_status, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (rc == 0 && e == cudaSuccess) e = cudaStreamSynchronize(st);
+  cudaFree(d_status);
+  RB200_CUDA(e);
+  if (rc != 0) return rc;
+  RB200_CHECK(h_status == 0, "g_idx must give every one of the %lld groups exactly %lld rows", (long long)groups,
+              (long long)(k / groups));
+  return 0;
+}
+
+int rb200_preprocess_weight_autogptq_perm(const void* qweight, void* dst, int64_t k, int64_t n, const int32_t* perm,
+                                          void* stream) {
+  RB200_CHECK(qweight && dst && perm, "qweight, dst and perm must be non-NULL");
+  RB200_CHECK(qweight != dst, "preprocess cannot run in place");
+  RB200_CHECK(n > 0 && k > 0 && n % 16 == 0 && k % 64 == 0, "preprocess needs n %% 16 == 0 and k %% 64 == 0 (n=%lld, k=%lld)",
+              (long long)n, (long long)k);
+  RB200_CHECK(aligned16(dst), "dst must be 16-byte aligned");
+  return preprocess_launch(qweight, dst, 1, k, n, 4, RB200_LAYOUT_AUTOGPTQ_KN, perm, static_cast<cudaStream_t>(stream));
+}
+
+int rb200_gather_columns(const void* x, const int32_t* perm, void* out, int64_t m, int64_t k, int64_t ldx, int64_t ldo,
+                         void* stream) {
+  RB200_CHECK(x && perm && out, "x, perm and out must be non-NULL");
+  RB200_CHECK(x != out, "gather cannot run in place");
+  RB200_CHECK(m >= 0 && k > 0 && ldx >= k && ldo >= k, "need ldx >= k and ldo >= k (k=%lld)", (long long)k);
+  return gather_columns_launch(x, perm, out, m, k, ldx, ldo, static_cast<cudaStream_t>(stream));
 }
 
 int rb200_unpack_zeros_autogptq(const void* zq, void* zeros_out, int64_t groups, int64_t n, void* stream) {
@@ -387,7 +426,7 @@ static int gemm_impl(const rb200_gemm_desc* d, const sk::ArCtx* ar, void* stream
     if (p.k % 64 == 0) {
       unsigned* flags = reinterpret_cast<unsigned*>(sc->counters) + kSkFlagOffset;
       return gemv_sk_run(p, d->weight_bits, zero_mode(d), sc->sm_count, sc->partials, sc->partial_bytes, flags,
-                         kSkFlagCount, ar, stream);
+                         kSkFlagCount, ar, nullptr, stream);
     }
     return gemv_cluster_run(p, d->weight_bits, zero_mode(d), sc->sm_count, stream);
   }
@@ -556,6 +595,26 @@ int rb200_group_gemm(const rb200_group_gemm_desc* d, void* stream_v) {
   const bool int_zero = d->zero_const >= 0.0f && d->zero_const <= 255.0f && d->zero_const == (float)(int)d->zero_const;
   const int zmode = (packed && (d->zeros || !int_zero)) ? kZeroGeneral : kZeroConstInt;
   const int64_t w_expert_bytes = d->n * d->k * d->weight_bits / 8;
+  if (packed && d->total_rows <= 32 && d->k % 64 == 0 && d->n % 16 == 0 && aligned16(d->x) && aligned16(d->out)) {
+    // Decode-size batch: the weights of an expert with rows are streamed once by the decode
+    // kernel (one launch per expert; a launch whose expert has no rows returns at once), instead
+    // of padding a handful of rows to a tensor-core tile of 192.
+    unsigned* flags = reinterpret_cast<unsigned*>(sc->counters) + kSkFlagOffset;
+    for (int e = 0; e < (int)d->num_experts; ++e) {
+      GemvParams pe = p;
+      pe.w = p.w + (int64_t)e * w_expert_bytes;
+      pe.s = p.s + (int64_t)e * d->scale_stride_e;
+      if (p.z) pe.z = p.z + (int64_t)e * d->scale_stride_e;
+      sk::GroupCtx g;
+      g.indptr = d->indptr;
+      g.expert = e;
+      g.has_prev = d->indptr_has_prev ? 1 : 0;
+      if (gemv_sk_run(pe, d->weight_bits, zmode, sc->sm_count, sc->partials, sc->partial_bytes, flags, kSkFlagCount,
+                      nullptr, &g, static_cast<cudaStream_t>(stream_v)) != 0)
+        return -1;
+    }
+    return 0;
+  }
   return umma_group_gemm_run(p, d->weight_bits, zmode, sc->sm_count, d->indptr, d->indptr_has_prev ? 1 : 0,
                              (int)d->num_experts, w_expert_bytes,
                              packed ? d->scale_stride_e : 0, static_cast<cudaStream_t>(stream_v));

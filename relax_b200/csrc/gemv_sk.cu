@@ -9,7 +9,7 @@
 namespace rb200 {
 
 int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float* partial, size_t partial_bytes,
-                unsigned* flags, size_t flag_count, const sk::ArCtx* ar, cudaStream_t stream) {
+                unsigned* flags, size_t flag_count, const sk::ArCtx* ar, const sk::GroupCtx* grp, cudaStream_t stream) {
   using namespace sk;
   const int frag = bits == 4 ? 64 : 32;
   const int chunk = frag * kBlocksPerChunk;
@@ -71,6 +71,10 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   pp.partial = partial;
   pp.flags = flags;
   pp.wait_limit_ms = wait_limit_ms();
+  if (grp) {
+    RB200_CHECK(!(ar && ar->world > 1), "the grouped form has no all-reduce epilogue");
+    pp.grp = *grp;
+  }
   if (ar && ar->world > 1) {
     RB200_CHECK(ar->world <= kArMaxRanks && ar->rank >= 0 && ar->rank < ar->world, "bad all-reduce rank %d / world %d",
                 ar->rank, ar->world);

@@ -102,9 +102,19 @@ __host__ __device__ __forceinline__ size_t ar_workspace_bytes(unsigned max_block
   return kArHeaderBytes + (size_t)2 * kArMaxRanks * max_blocks * kArSlotWords * 8;
 }
 
+// Grouped (expert) form at decode size: one launch per expert over the same x / out; the rows
+// [indptr[expert - 1], indptr[expert]) of x are that expert's batch (indptr on the device, end
+// offsets).  A launch whose expert has no rows returns at once.
+struct GroupCtx {
+  const int64_t* indptr;  // nullptr: the ungrouped form, rows [0, m)
+  int expert;
+  int has_prev;           // expert 0 starts at indptr[-1] (a sub-range of a longer table), not at row 0
+};
+
 struct Params {
   GemvParams g;
   ArCtx ar;
+  GroupCtx grp;
   float* partial;     // [grid][2][8 warps][MT][4][32] fp32: slot 0 tail piece (for the owner), slot 1 own head piece
   unsigned* flags;    // [grid][8]: 1 while a tail piece waits for its owner, 0 at rest
   int has_z_tile;
@@ -260,6 +270,18 @@ __global__ void __launch_bounds__(kThreads, 2)
   __syncthreads();
   griddep_launch_dependents();
 
+  // batch rows of this launch inside x / out
+  int m_lo = 0, m_rows = p.m;
+  if (pp.grp.indptr) {
+    griddep_wait();  // the row table is the routing kernel's output
+    const int64_t r0 = (pp.grp.expert || pp.grp.has_prev) ? pp.grp.indptr[pp.grp.expert - 1] : 0;
+    int64_t r1 = pp.grp.indptr[pp.grp.expert];
+    if (r1 > p.m) r1 = p.m;  // never past the rows x / out hold
+    if (r1 <= r0) return;    // every thread of every CTA alike; nothing is in flight yet
+    m_lo = (int)r0;
+    m_rows = (int)(r1 - r0) < MT * 8 ? (int)(r1 - r0) : MT * 8;
+  }
+
   const int cta = blockIdx.x;
   const unsigned total = (unsigned)p.total_iters;  // the host checks that total * grid fits 32 bits
   const unsigned grid = gridDim.x;
@@ -300,7 +322,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
   };
   auto feed_x = [&](int chunk, int stage) {  // one lane: the x tile of the stage
-    tma_load_3d(smem + (size_t)stage * kStage + G::kWBytes, &tmap_x, 0, 0, chunk * G::kXBlocks, &full_bar[stage]);
+    tma_load_3d(smem + (size_t)stage * kStage + G::kWBytes, &tmap_x, 0, m_lo, chunk * G::kXBlocks, &full_bar[stage]);
   };
   // Walker over this CTA's (tile, chunk) stages in execution order.
   struct Walker {
@@ -384,7 +406,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           const int64_t m = mt * 8 + t * 2 + cc;
-          if (m < p.m) p.out[m * p.ldo + f] = __float2half_rn(silu_mul(v[mt][cc], v[mt][cc + 2]));
+          if (m < m_rows) p.out[(m_lo + m) * p.ldo + f] = __float2half_rn(silu_mul(v[mt][cc], v[mt][cc + 2]));
         }
       return;
     }
@@ -395,7 +417,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       for (int c = 0; c < 4; ++c) {
         const int64_t m = mt * 8 + t * 2 + (c & 1);
         const int64_t n = n0 + (c >> 1) * 8;
-        if (m < p.m) p.out[m * p.ldo + n] = __float2half_rn(apply_epilogue(v[mt][c], p.epi, m, n));
+        if (m < m_rows) p.out[(m_lo + m) * p.ldo + n] = __float2half_rn(apply_epilogue(v[mt][c], p.epi, m_lo + m, n));
       }
   };
 
@@ -771,7 +793,9 @@ int launch_sk_i8(const Params& pp, const Launch& l, const CUtensorMap& tx, const
 // Host entry: plans and launches the stream-k decode kernel.  `partial` / `flags` are scratch;
 // the flags must be zero before the first launch and are left zero by every launch.
 // `ar` (may be nullptr): finish the call with the sum over ranks, see sk::ArCtx.
+// `grp` (may be nullptr): one expert of the grouped form, see sk::GroupCtx; p.m is then the total
+// row count of x / out (at most 32).
 int gemv_sk_run(const GemvParams& p, int bits, int zmode, int sm_count, float* partial, size_t partial_bytes,
-                unsigned* flags, size_t flag_count, const sk::ArCtx* ar, cudaStream_t stream);
+                unsigned* flags, size_t flag_count, const sk::ArCtx* ar, const sk::GroupCtx* grp, cudaStream_t stream);
 
 }  // namespace rb200

@@ -284,10 +284,58 @@ int pf_preprocess_q4f16(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret
 int pf_preprocess_autogptq(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
   Args a{v, tc, n, "relax_b200.preprocess_weight_autogptq"};
   const DLTensor *w, *out;
-  PF_CHECK(n == 2, "%s expects (qweight, out), got %d arguments", a.fname, n);
+  PF_CHECK(n == 2 || n == 3, "%s expects (qweight, out[, perm]), got %d arguments", a.fname, n);
   if (a.tensor(0, &w) || a.tensor(1, &out)) return -1;
   if (ret_tc) *ret_tc = RB200_ARG_NULL;
-  return preprocess_common(a.fname, w, out, true, RB200_LAYOUT_AUTOGPTQ_KN);
+  if (n == 2 || a.is_null(2)) return preprocess_common(a.fname, w, out, true, RB200_LAYOUT_AUTOGPTQ_KN);
+  // act-order: the reduction axis permuted through perm (from relax_b200.gptq_act_order)
+  const DLTensor* perm;
+  if (a.tensor(2, &perm)) return -1;
+  PF_CHECK(w->ndim == 2 && (is_dtype(w, kDLUInt, 32) || is_dtype(w, kDLInt, 32)) && compact(w) &&
+               w->device.device_type == kDLCUDA,
+           "%s: with perm, qweight must be a compact uint32 [K/8, N] CUDA tensor", a.fname);
+  PF_CHECK(out->ndim == 2 && out->shape[0] == w->shape[0] && out->shape[1] == w->shape[1] &&
+               out->dtype.bits == 32 && compact(out) && out->device.device_type == kDLCUDA,
+           "%s: out must match qweight", a.fname);
+  if (check_tensor(a.fname, "perm", perm, kDLInt, 32)) return -1;
+  PF_CHECK(perm->ndim == 1 && perm->shape[0] == w->shape[0] * 8, "%s: perm must be int32 [K]", a.fname);
+  return rb200_preprocess_weight_autogptq_perm(data_of(w), data_of(out), w->shape[0] * 8, w->shape[1],
+                                               static_cast<const int32_t*>(data_of(perm)), rb200_get_stream());
+}
+// (g_idx i32 [K], groups:int, perm_out i32 [K])
+int pf_gptq_act_order(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "relax_b200.gptq_act_order"};
+  const DLTensor *g_idx, *perm;
+  int64_t groups = 0;
+  PF_CHECK(n == 3, "%s expects (g_idx, groups, perm_out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &g_idx) || a.integer(1, &groups) || a.tensor(2, &perm)) return -1;
+  if (check_tensor(a.fname, "g_idx", g_idx, kDLInt, 32) || check_tensor(a.fname, "perm_out", perm, kDLInt, 32)) return -1;
+  PF_CHECK(g_idx->ndim == 1 && perm->ndim == 1 && perm->shape[0] == g_idx->shape[0], "%s: g_idx and perm_out must be int32 [K]",
+           a.fname);
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_gptq_act_order(static_cast<const int32_t*>(data_of(g_idx)), g_idx->shape[0], groups,
+                              static_cast<int32_t*>(data_of(perm)), rb200_get_stream());
+}
+// (x f16 [..., K], perm i32 [K], out f16 like x): out[..., j] = x[..., perm[j]]
+int pf_gather_columns(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
+  Args a{v, tc, n, "relax_b200.gather_columns"};
+  const DLTensor *x, *perm, *out;
+  PF_CHECK(n == 3, "%s expects (x, perm, out), got %d arguments", a.fname, n);
+  if (a.tensor(0, &x) || a.tensor(1, &perm) || a.tensor(2, &out)) return -1;
+  if (check_tensor(a.fname, "x", x, kDLFloat, 16) || check_tensor(a.fname, "perm", perm, kDLInt, 32) ||
+      check_tensor(a.fname, "out", out, kDLFloat, 16))
+    return -1;
+  PF_CHECK(x->ndim >= 1 && perm->ndim == 1 && perm->shape[0] == x->shape[x->ndim - 1], "%s: perm must be int32 [K]", a.fname);
+  PF_CHECK(out->ndim == x->ndim, "%s: out must have the shape of x", a.fname);
+  int64_t m = 1;
+  for (int i = 0; i < x->ndim; ++i) {
+    PF_CHECK(out->shape[i] == x->shape[i], "%s: out must have the shape of x", a.fname);
+    if (i + 1 < x->ndim) m *= x->shape[i];
+  }
+  const int64_t k = perm->shape[0];
+  if (ret_tc) *ret_tc = RB200_ARG_NULL;
+  return rb200_gather_columns(data_of(x), static_cast<const int32_t*>(data_of(perm)), data_of(out), m, k, k, k,
+                              rb200_get_stream());
 }
 // (qzeros u32 [G, N/8], out f16 [G, N])
 int pf_unpack_zeros_autogptq(RB200Value* v, int* tc, int n, RB200Value* ret, int* ret_tc, void*) {
@@ -739,6 +787,8 @@ void ensure_builtins() {
   register_builtin("relax_b200.interleave_gate_up", pf_interleave_gate_up);
   register_builtin("relax_b200.preprocess_weight_autogptq", pf_preprocess_autogptq);
   register_builtin("relax_b200.unpack_zeros_autogptq", pf_unpack_zeros_autogptq);
+  register_builtin("relax_b200.gptq_act_order", pf_gptq_act_order);
+  register_builtin("relax_b200.gather_columns", pf_gather_columns);
   register_builtin("relax_b200.gemm_fp16_autogptq", pf_gemm_autogptq);
   register_builtin("cutlass.ft_gemm_fp16_int4", pf_ft_gemm_int4);
   register_builtin("cutlass.ft_gemm_fp16_int8", pf_ft_gemm_int8);

@@ -50,7 +50,8 @@ __host__ __device__ __forceinline__ int64_t gate_up_source_row(int64_t j, int64_
 
 template <int BITS, int LAYOUT>
 __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
-                              int64_t K, int64_t N, int64_t units_per_expert, int64_t total_units, int interleave) {
+                              int64_t K, int64_t N, int64_t units_per_expert, int64_t total_units, int interleave,
+                              const int32_t* __restrict__ k_perm) {
   constexpr int kFrag = BITS == 4 ? 64 : 32;
   const int64_t expert_bytes = K * N * BITS / 8;
   for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total_units;
@@ -98,7 +99,9 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
         for (int p = 0; p < 8; ++p) {
           int64_t srow = nb * 16 + g + row_of[p];
           if (interleave) srow = gate_up_source_row(srow, N);
-          uint32_t c = load_code<BITS, LAYOUT>(s, srow, k0 + 4 * j + k_of[p], K, N);
+          int64_t ks = k0 + 4 * j + k_of[p];
+          if (LAYOUT == 2 && k_perm) ks = k_perm[ks];  // act-order: k position -> source row
+          uint32_t c = load_code<BITS, LAYOUT>(s, srow, ks, K, N);
           w |= c << (4 * p);
         }
         words[j] = w;
@@ -213,6 +216,45 @@ __global__ void __launch_bounds__(256) repack_ft_panel_kernel(const uint8_t* __r
   }
 }
 
+// Act-order AutoGPTQ weights (tests/python/dlight/test_gpu_gemv.py:639-649 reads scale and zero
+// of element k through g_idx[k]): perm lists the k rows group by group, in their original order
+// inside a group, so that the weight repacked through perm has its groups contiguous along k and
+// the matmul of x gathered through the same perm equals the reference's.  One CTA; every thread
+// owns groups g = tid, tid + blockDim, ... and scans g_idx twice (count, then place).
+// status: 0 = fine, 1 = some group does not have exactly K / G members or an index is out of range.
+__global__ void gptq_act_order_kernel(const int32_t* __restrict__ g_idx, int K, int G, int32_t* __restrict__ perm,
+                                      int* __restrict__ status) {
+  extern __shared__ int s_start[];  // [G + 1]
+  const int per = K / G;
+  __shared__ int bad;
+  if (threadIdx.x == 0) bad = 0;
+  __syncthreads();
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    int c = 0;
+    for (int k = 0; k < K; ++k) c += g_idx[k] == g;
+    if (c != per) bad = 1;
+    s_start[g] = g * per;  // groups of equal size, or the result is rejected
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *status = bad;
+  if (bad) return;
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    int pos = s_start[g];
+    for (int k = 0; k < K; ++k)
+      if (g_idx[k] == g) perm[pos++] = k;
+  }
+}
+
+// out[m, j] = x[m, perm[j]] over fp16
+__global__ void gather_columns_kernel(const __half* __restrict__ x, const int32_t* __restrict__ perm,
+                                      __half* __restrict__ out, int64_t M, int64_t K, int64_t ldx, int64_t ldo) {
+  const int64_t total = M * K;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / K, j = i % K;
+    out[m * ldo + j] = x[m * ldx + perm[j]];
+  }
+}
+
 }  // namespace
 
 // dst[o][j][i] = src[o][gate_up_source_row(j)][i] over fp16 elements: the row permutation of the
@@ -227,9 +269,10 @@ __global__ void interleave_rows_kernel(const __half* __restrict__ src, __half* _
 }
 
 int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, int64_t n, int bits,
-                      int layout_flags, cudaStream_t stream) {
+                      int layout_flags, const int32_t* k_perm, cudaStream_t stream) {
   const int interleave = (layout_flags & 0x100) ? 1 : 0;
   const int layout = layout_flags & 0xff;
+  RB200_CHECK(!k_perm || layout == 2, "a k permutation goes with the AutoGPTQ source layout only");
   const int64_t units = k * n * bits / 8 / 16;
   const int64_t total = units * experts;
   const int threads = 256;
@@ -250,15 +293,16 @@ int preprocess_launch(const void* src, void* dst, int64_t experts, int64_t k, in
     return 0;
   }
   if (bits == 4 && layout == 0)
-    repack_kernel<4, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
+    repack_kernel<4, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave, k_perm);
   else if (bits == 4 && layout == 1)
-    repack_kernel<4, 1><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
+    repack_kernel<4, 1><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave, k_perm);
   else if (bits == 4 && layout == 2)
-    repack_kernel<4, 2><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
+    repack_kernel<4, 2><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave, k_perm);
   else if (bits == 8 && layout == 0)
-    repack_kernel<8, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave);
+    repack_kernel<8, 0><<<(int)blocks, threads, 0, stream>>>(s, d, k, n, units, total, interleave, k_perm);
   else
     RB200_CHECK(false, "unsupported preprocess combination bits=%d layout=%d", bits, layout);
+
   RB200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -270,6 +314,25 @@ int interleave_rows_launch(const void* src, void* dst, int64_t outer, int64_t n,
   if (blocks > (int64_t)sm_count_current() * 16) blocks = (int64_t)sm_count_current() * 16;
   interleave_rows_kernel<<<(int)blocks, 256, 0, stream>>>(static_cast<const __half*>(src), static_cast<__half*>(dst),
                                                          outer, n, inner);
+  RB200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int gptq_act_order_launch(const int32_t* g_idx, int64_t k, int64_t groups, int32_t* perm, int* status,
+                          cudaStream_t stream) {
+  gptq_act_order_kernel<<<1, 1024, (size_t)(groups + 1) * sizeof(int), stream>>>(g_idx, (int)k, (int)groups, perm, status);
+  RB200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int gather_columns_launch(const void* x, const int32_t* perm, void* out, int64_t m, int64_t k, int64_t ldx,
+                          int64_t ldo, cudaStream_t stream) {
+  const int64_t total = m * k;
+  if (total == 0) return 0;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > (int64_t)sm_count_current() * 16) blocks = (int64_t)sm_count_current() * 16;
+  gather_columns_kernel<<<(int)blocks, 256, 0, stream>>>(static_cast<const __half*>(x), perm, static_cast<__half*>(out),
+                                                        m, k, ldx, ldo);
   RB200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -107,10 +107,32 @@ def moe_gemm_q4f16(x, w_pre, scales, indptr, zeros=None, group_size: int = 32, z
     return out
 
 
-def preprocess_weight_autogptq(qweight: torch.Tensor) -> torch.Tensor:
+def gptq_act_order(g_idx: torch.Tensor, groups: int) -> torch.Tensor:
+    """Permutation of the reduction axis that makes the groups of an act-order AutoGPTQ weight
+    contiguous: ``perm`` int32 [K] lists the k rows group by group (original order inside a group).
+    Raises when a group does not have exactly ``K / groups`` rows."""
+    g = g_idx.to(device=g_idx.device, dtype=torch.int32).contiguous()
+    perm = torch.empty_like(g)
+    get_global_func("relax_b200.gptq_act_order")(g, int(groups), perm)
+    return perm
+
+
+def gather_columns(x: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
+    """``x[..., perm]`` for fp16 ``x`` (the activation side of an act-order weight)."""
+    out = torch.empty_like(x)
+    get_global_func("relax_b200.gather_columns")(x.contiguous(), perm, out)
+    return out
+
+
+def preprocess_weight_autogptq(qweight: torch.Tensor, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Repack an AutoGPTQ weight (uint32 [K/8, N], 8 k-consecutive nibbles per word:
-    tests/python/dlight/test_gpu_gemv.py:639-649)."""
-    return get_global_func("relax_b200.preprocess_weight_autogptq")(qweight)
+    tests/python/dlight/test_gpu_gemv.py:639-649).  ``perm`` (from :func:`gptq_act_order`) puts
+    source row ``perm[j]`` at position ``j`` of the reduction axis."""
+    if perm is None:
+        return get_global_func("relax_b200.preprocess_weight_autogptq")(qweight)
+    out = torch.empty_like(qweight)
+    get_global_func("relax_b200.preprocess_weight_autogptq", raw=True)(qweight, out, perm)
+    return out
 
 
 def unpack_zeros_autogptq(qzeros: torch.Tensor) -> torch.Tensor:
@@ -121,17 +143,21 @@ def unpack_zeros_autogptq(qzeros: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def gemm_fp16_autogptq(x, w_pre, scales, zeros, bias=None, g_idx=None,
+def gemm_fp16_autogptq(x, w_pre, scales, zeros, bias=None, g_idx=None, perm=None,
                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``bias + x @ ((q - zeros) * scales)`` for AutoGPTQ weights: ``w_pre`` from
+    """``bias + x @ ((q - zeros[g_idx]) * scales[g_idx])`` for AutoGPTQ weights
+    (tests/python/dlight/test_gpu_gemv.py:639-661): ``w_pre`` from
     :func:`preprocess_weight_autogptq`, ``scales`` fp16 [G, N], ``zeros`` fp16 [G, N] from
-    :func:`unpack_zeros_autogptq`.  Groups run in order along k; a ``g_idx`` that is not
-    ``k // group_size`` (activation reordering) is rejected."""
+    :func:`unpack_zeros_autogptq`.  With groups in order along k (``g_idx = k // group_size``)
+    nothing else is needed.  For an act-order weight pass the ``perm`` that ``w_pre`` was repacked
+    with: ``x`` is gathered through it first.  A reordered ``g_idx`` without ``perm`` is rejected."""
     k, n = w_pre.shape[0] * 8, w_pre.shape[1]
-    if g_idx is not None:
+    if perm is not None:
+        x = gather_columns(x, perm)
+    elif g_idx is not None:
         expect = torch.arange(k, device=g_idx.device) // (k // scales.shape[0])
         if not torch.equal(g_idx.to(torch.int64), expect):
-            raise ValueError("g_idx must be k // group_size: reordered groups are not supported")
+            raise ValueError("g_idx reorders the groups: repack the weight with gptq_act_order's perm and pass perm")
     if out is None:
         out = torch.empty(*x.shape[:-1], n, dtype=torch.float16, device=x.device)
     get_global_func("relax_b200.gemm_fp16_autogptq")(x, w_pre, scales, zeros, bias, out)

@@ -60,3 +60,51 @@ def test_autogptq_reordered_groups_are_rejected():
     bad = torch.from_numpy(g_idx[::-1].astype(np.int64).copy())
     with pytest.raises(ValueError):
         ops.gemm_fp16_autogptq(to_dev(x), pre, to_dev(scales), zeros, g_idx=bad)
+
+
+def _act_order_g_idx(seed, k, group):
+    """An activation-ordered g_idx: row k belongs to group rank(k) // group for a random ranking,
+    the form AutoGPTQ writes with desc_act; every group has exactly `group` rows."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    rank = g.permutation(k)
+    return (rank // group).astype(np.uint32)
+
+
+@pytest.mark.parametrize("k,n,group", [(256, 64, 128), (4096, 512, 128), (1024, 256, 64)])
+def test_act_order_dequant_bit_exact(oracle, k, n, group):
+    """wq[perm[j], n] of the reference decode (scales and zeros through g_idx,
+    tests/python/dlight/test_gpu_gemv.py:646-648) = row j of the repacked weight, bit for bit."""
+    qweight, qzeros, scales, _, _, _ = _case(7 * k + n, 1, k, n, group)
+    g_idx = _act_order_g_idx(k + 1, k, group)
+    perm = ops.gptq_act_order(torch.from_numpy(g_idx.astype(np.int32)).cuda(), k // group)
+    perm_h = perm.cpu().numpy()
+    # stable: group by group, original order inside a group
+    assert np.array_equal(perm_h, np.argsort(g_idx, kind="stable").astype(np.int32))
+    pre = ops.preprocess_weight_autogptq(u32_to_dev(qweight), perm=perm)
+    zeros = ops.unpack_zeros_autogptq(u32_to_dev(qzeros))
+    wq = ops.dequantize(pre, to_dev(scales), n, k, 4, ops.LAYOUT_FT_KN, zeros=zeros, group_size=group, zero_const=0.0)
+    torch.cuda.synchronize()
+    exp_kn = oracle.C().decode_autogptq(qweight, qzeros, scales, g_idx)
+    assert np.array_equal(bits16(wq.cpu().numpy()), bits16(np.ascontiguousarray(exp_kn[perm_h].T)))
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (8, 512, 256), (300, 512, 256)])
+def test_act_order_matmul(oracle, m, k, n):
+    qweight, qzeros, scales, _, x, bias = _case(m * 5 + k, m, k, n)
+    g_idx = _act_order_g_idx(m + k, k, 128)
+    perm = ops.gptq_act_order(torch.from_numpy(g_idx.astype(np.int32)).cuda(), k // 128)
+    pre = ops.preprocess_weight_autogptq(u32_to_dev(qweight), perm=perm)
+    zeros = ops.unpack_zeros_autogptq(u32_to_dev(qzeros))
+    out = ops.gemm_fp16_autogptq(to_dev(x), pre, to_dev(scales), zeros, bias=to_dev(bias), perm=perm)
+    torch.cuda.synchronize()
+    _check_status()
+    C = oracle.C()
+    wq_kn = C.decode_autogptq(qweight, qzeros, scales, g_idx)
+    exp = C.epilogue(C.matmul_f32(x, wq_kn, False), bias)
+    assert_close(out.cpu().numpy(), exp)
+
+
+def test_act_order_uneven_groups_are_rejected():
+    g_idx = np.zeros(256, dtype=np.int32)  # every row in group 0 of 2
+    with pytest.raises(RuntimeError):
+        ops.gptq_act_order(torch.from_numpy(g_idx).cuda(), 2)

@@ -89,3 +89,54 @@ def test_moe_gemm_q4f16_layout(oracle, group, asym):
     C = oracle.C()
     wq = np.stack([C.decode_q4_nk(cases[e].w, cases[e].scales, cases[e].zeros, 7.0, group) for e in range(E)])
     assert_close(out.cpu().numpy(), _oracle_grouped(oracle, x, wq, indptr))
+
+
+@pytest.mark.parametrize("bits,group,rows", [
+    (4, 128, [1, 0, 1, 0, 0, 2, 0, 0]),     # two tokens, top-2 of eight experts
+    (4, -1, [0, 0, 0, 0, 0, 0, 0, 1]),
+    (8, 64, [3, 9, 0, 5]),
+    (4, 64, [8, 8, 8, 8]),                  # exactly 32 rows: still the decode-size path
+    (8, -1, [0, 31, 0, 1]),
+])
+def test_moe_gemm_decode_size_batches(oracle, bits, group, rows):
+    """At most 32 rows in all: every expert with rows is one launch of the decode kernel over
+    its own weights (rows taken from indptr on the device); experts without rows launch and
+    return.  Same oracle as the large-batch form."""
+    g = np.random.Generator(np.random.PCG64(bits * 1000 + max(group, 0) + sum(rows)))
+    E, K, N = len(rows), 512, 384
+    indptr = np.cumsum(rows).astype(np.int64)
+    x = g.standard_normal((sum(rows), K), dtype=np.float32).astype(np.float16)
+    w = g.integers(-128, 128, size=(E, K, N // 2 if bits == 4 else N), dtype=np.int8)
+    kg = 1 if group <= 0 else K // group
+    scales = g.uniform(0.001, 0.01, size=(E, kg, N) if group > 0 else (E, N)).astype(np.float16)
+    pre = ops.preprocess_weight_ft(to_dev(w), bits == 4)
+    out = torch.full((sum(rows), N), float("nan"), dtype=torch.float16, device="cuda")
+    ops.moe_gemm_ft(to_dev(x), pre, to_dev(scales), torch.from_numpy(indptr).cuda(), out=out)
+    torch.cuda.synchronize()
+    _check_status()
+    C = oracle.C()
+    wq = np.stack([np.ascontiguousarray(C.decode_ft_kn(w[e], scales[e], bits, group).T) for e in range(E)])
+    assert_close(out.cpu().numpy(), _oracle_grouped(oracle, x, wq, indptr))
+
+
+def test_moe_gemm_decode_size_expert_sub_range(oracle):
+    """A rank that owns experts [2, 4) of a longer routing table passes indptr + 2 with
+    indptr_has_prev: its first expert starts at indptr[1], not at row 0."""
+    g = np.random.Generator(np.random.PCG64(77))
+    E, K, N = 4, 256, 256
+    rows = [2, 1, 3, 2]
+    indptr = np.cumsum(rows).astype(np.int64)
+    x = g.standard_normal((sum(rows), K), dtype=np.float32).astype(np.float16)
+    w = g.integers(-128, 128, size=(E, K, N // 2), dtype=np.int8)
+    scales = g.uniform(0.001, 0.01, size=(E, N)).astype(np.float16)
+    pre = ops.preprocess_weight_ft(to_dev(w), True)
+    out = torch.zeros((sum(rows), N), dtype=torch.float16, device="cuda")
+    ops.moe_gemm_ft(to_dev(x), pre[2:], to_dev(scales[2:]), torch.from_numpy(indptr).cuda(), out=out, first_expert=2)
+    torch.cuda.synchronize()
+    _check_status()
+    C = oracle.C()
+    wq = np.stack([np.ascontiguousarray(C.decode_ft_kn(w[e], scales[e], 4, -1).T) for e in range(E)])
+    exp = _oracle_grouped(oracle, x, wq, indptr)
+    got = out.cpu().numpy()
+    assert_close(got[3:], exp[3:])
+    assert not got[:3].any()  # rows of the experts this rank does not own are left alone
