@@ -377,6 +377,17 @@ RB200_API int rb200_gemm_fp16_intx_allreduce(const rb200_gemm_desc* desc, void* 
                                              int64_t max_n, void* stream);
 
 /*
+ * Self-test of the fused form on ONE GPU: all `world` ranks run inside one cooperative launch
+ * (every rank on its share of the SMs, all CTAs resident together, so ranks that wait on one
+ * another cannot starve each other).  Every rank computes desc's matmul on the same x and
+ * weights; rank r writes rows [r * m, (r + 1) * m) of desc->out, which therefore needs world * m
+ * rows and must equal epilogue(world * (x @ W^T)) in every block of rows.  workspaces: `world`
+ * zero-filled local buffers of rb200_gemm_allreduce_workspace_bytes(max_n) bytes.
+ */
+RB200_API int rb200_gemm_fp16_intx_allreduce_selftest(const rb200_gemm_desc* desc, void* const* workspaces, int world,
+                                                      int64_t max_n, void* stream);
+
+/*
  * Debug/verification entry: writes the dequantised weight wq fp16 [n, k] (row-major) that the
  * matmul kernels feed to the tensor cores, produced by the same device decode routine.  Uses
  * the w / scales / zeros / group / stride / zero_const fields of the descriptor.  The arithmetic

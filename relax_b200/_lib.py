@@ -101,6 +101,7 @@ SIGNATURES = {
     "rb200_gemm_fp16_intx_noalloc": (_I, [ctypes.POINTER(GemmDesc), _V]),
     "rb200_gemm_allreduce_workspace_bytes": (ctypes.c_size_t, [_I64]),
     "rb200_gemm_fp16_intx_allreduce": (_I, [ctypes.POINTER(GemmDesc), ctypes.POINTER(_V), _I, _I, _I64, _V]),
+    "rb200_gemm_fp16_intx_allreduce_selftest": (_I, [ctypes.POINTER(GemmDesc), ctypes.POINTER(_V), _I, _I64, _V]),
     "rb200_gemm_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64, _I]),
     "rb200_gemm_fp16_int_bias_act": (_I, [_V, _V, _V, _V, _V, _S, _I, _I, _I, _I, _I, _I, _V,
                                           ctypes.c_size_t, _V]),

@@ -499,6 +499,23 @@ int rb200_gemm_fp16_intx_allreduce(const rb200_gemm_desc* d, void* const* worksp
   return gemm_impl(d, &ar, stream_v);
 }
 
+int rb200_gemm_fp16_intx_allreduce_selftest(const rb200_gemm_desc* d, void* const* workspaces, int world,
+                                            int64_t max_n, void* stream_v) {
+  RB200_CHECK(world >= 2 && world <= sk::kArMaxRanks, "world=%d outside [2, %d]", world, sk::kArMaxRanks);
+  RB200_CHECK(workspaces != nullptr && max_n > 0, "workspaces must be non-NULL and max_n positive");
+  sk::ArCtx ar;
+  memset(&ar, 0, sizeof(ar));
+  for (int i = 0; i < world; ++i) {
+    RB200_CHECK(workspaces[i] != nullptr, "workspace of rank %d is NULL", i);
+    ar.ws[i] = static_cast<uint8_t*>(workspaces[i]);
+  }
+  ar.rank = 0;
+  ar.world = world;
+  ar.emulate = world;
+  ar.max_blocks = (unsigned)((max_n + 15) / 16);
+  return gemm_impl(d, &ar, stream_v);
+}
+
 static int fill_ft_desc(rb200_gemm_desc* d, const void* A, const void* B, const void* scales,
                         const void* bias, const void* residual, void* out, int m, int n, int k,
                         int group_size, int bias_stride, int weight_bits, void* workspace,

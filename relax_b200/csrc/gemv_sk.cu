@@ -60,10 +60,15 @@ int gemv_sk_run(const GemvParams& p_in, int bits, int zmode, int sm_count, float
   if (stages < 2) stages = 2;
   p.stages = stages;
   l.smem_bytes = 1024 + (size_t)stages * sb + (size_t)(stages + 1) * 2 * sizeof(uint64_t);  // 1 KB: alignment slack
-  long long grid = (long long)sm_count * ctas_per_sm;
+  // self-test with several ranks in one launch: every rank gets an equal share of the SMs
+  const int emulate = (ar && ar->world > 1 && ar->emulate > 1) ? ar->emulate : 1;
+  RB200_CHECK(emulate == 1 || emulate == ar->world, "emulate=%d must equal world=%d", emulate, ar ? ar->world : 0);
+  long long grid = (long long)(sm_count / emulate) * ctas_per_sm;
   if (grid > p.total_iters) grid = p.total_iters;
-  l.grid = (int)grid;
+  RB200_CHECK(grid >= 1, "no SMs left per emulated rank");
   RB200_CHECK(p.total_iters * grid < (1ll << 31), "problem too large for the decode kernel's 32-bit work split");
+  l.grid = (int)grid * emulate;
+  l.cooperative = emulate > 1 ? 1 : 0;
 
   const size_t need = (size_t)l.grid * 2 * kConsumerWarps * l.mt * 128 * sizeof(float);
   RB200_CHECK(partial_bytes >= need && flag_count >= (size_t)l.grid * kConsumerWarps,

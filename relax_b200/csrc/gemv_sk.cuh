@@ -97,6 +97,11 @@ struct ArCtx {
   uint8_t* ws[kArMaxRanks];  // ws[r]: rank r's workspace as this GPU addresses it
   int rank, world;           // world <= 1: no exchange
   unsigned max_blocks;       // 16-row blocks a region has room for
+  // self-test on one GPU: the launch holds `emulate` ranks, every one gridDim / emulate CTAs
+  // (launched cooperatively, so that all of them are resident while they wait on one another);
+  // CTA b belongs to rank b / (gridDim / emulate), which uses its own slice of the split-k
+  // scratch and writes rows [rank * m, (rank + 1) * m) of out.  0: an ordinary launch.
+  int emulate;
 };
 __host__ __device__ __forceinline__ size_t ar_workspace_bytes(unsigned max_blocks) {
   return kArHeaderBytes + (size_t)2 * kArMaxRanks * max_blocks * kArSlotWords * 8;
@@ -282,9 +287,22 @@ __global__ void __launch_bounds__(kThreads, 2)
     m_rows = (int)(r1 - r0) < MT * 8 ? (int)(r1 - r0) : MT * 8;
   }
 
-  const int cta = blockIdx.x;
+  // rank-dependent values (one launch = one rank, except in the self-test: see ArCtx::emulate)
+  int ar_rank = pp.ar.rank;
+  unsigned grid = gridDim.x;
+  int cta = blockIdx.x;
+  float* sk_partial = pp.partial;
+  unsigned* sk_flags = pp.flags;
+  __half* out_base = p.out;
+  if (AR && pp.ar.emulate > 1) {
+    grid = gridDim.x / (unsigned)pp.ar.emulate;
+    ar_rank = (int)(blockIdx.x / grid);
+    cta = (int)(blockIdx.x % grid);
+    sk_partial += (size_t)ar_rank * grid * 2 * kConsumerWarps * MT * 128;
+    sk_flags += (size_t)ar_rank * grid * kConsumerWarps;
+    out_base += (size_t)ar_rank * p.m * p.ldo;
+  }
   const unsigned total = (unsigned)p.total_iters;  // the host checks that total * grid fits 32 bits
-  const unsigned grid = gridDim.x;
   const int cpt = p.chunks_per_tile;
   PiecePlan plan;
   plan.build((unsigned)cta, total, grid, cpt);
@@ -406,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           const int64_t m = mt * 8 + t * 2 + cc;
-          if (m < m_rows) p.out[(m_lo + m) * p.ldo + f] = __float2half_rn(silu_mul(v[mt][cc], v[mt][cc + 2]));
+          if (m < m_rows) out_base[(m_lo + m) * p.ldo + f] = __float2half_rn(silu_mul(v[mt][cc], v[mt][cc + 2]));
         }
       return;
     }
@@ -417,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       for (int c = 0; c < 4; ++c) {
         const int64_t m = mt * 8 + t * 2 + (c & 1);
         const int64_t n = n0 + (c >> 1) * 8;
-        if (m < m_rows) p.out[(m_lo + m) * p.ldo + n] = __float2half_rn(apply_epilogue(v[mt][c], p.epi, m_lo + m, n));
+        if (m < m_rows) out_base[(m_lo + m) * p.ldo + n] = __float2half_rn(apply_epilogue(v[mt][c], p.epi, m_lo + m, n));
       }
   };
 
@@ -433,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int blk = tile_i * kConsumerWarps + warp;
     if (blk >= n_blocks) return;
     for (int r = 0; r < pp.ar.world; ++r) {
-      uint2* dst = ar_slot(r, ar_call, pp.ar.rank, blk) + lane;
+      uint2* dst = ar_slot(r, ar_call, ar_rank, blk) + lane;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -450,34 +468,48 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
       for (int c = 0; c < 4; ++c) sum[mt][c] = 0.0f;
     bool arrived = true;
-    for (int r = 0; r < pp.ar.world && arrived; ++r) {
-      const uint2* src = ar_slot(pp.ar.rank, ar_call, r, blk) + lane;
-      uint2 w[MT][4];
+    // the words of several ranks are requested together (as many as the register file takes),
+    // so that the sum over eight ranks costs two to four memory round trips, not eight
+    constexpr int kRanksPerBatch = 8 / MT;
+    for (int r0 = 0; r0 < pp.ar.world && arrived; r0 += kRanksPerBatch) {
+      uint2 w[kRanksPerBatch][MT][4];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+      for (int i = 0; i < kRanksPerBatch; ++i) {
+        if (r0 + i < pp.ar.world) {
+          const uint2* src = ar_slot(ar_rank, ar_call, r0 + i, blk) + lane;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) w[mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
+          for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (w[mt][c].y != ar_call) {  // not there yet: poll this word
-            unsigned long long t0;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-            do {
-              w[mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
-              unsigned long long t1;
-              asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-              if (t1 - t0 > limit_ns) {
-                if (p.status) atomicExch(p.status, kStatusWaitTimeout);
-                arrived = false;
-                break;
-              }
-            } while (w[mt][c].y != ar_call);
-          }
-          sum[mt][c] += __uint_as_float(w[mt][c].x);
+            for (int c = 0; c < 4; ++c) w[i][mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
         }
-      arrived = __all_sync(0xffffffffu, arrived);
+      }
+#pragma unroll
+      for (int i = 0; i < kRanksPerBatch; ++i) {
+        if (r0 + i < pp.ar.world && arrived) {
+          const uint2* src = ar_slot(ar_rank, ar_call, r0 + i, blk) + lane;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              if (arrived && w[i][mt][c].y != ar_call) {  // not there yet: poll this word
+                unsigned long long t0;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+                do {
+                  w[i][mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
+                  unsigned long long t1;
+                  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                  if (t1 - t0 > limit_ns) {
+                    if (p.status) atomicExch(p.status, kStatusWaitTimeout);
+                    arrived = false;
+                    break;
+                  }
+                } while (w[i][mt][c].y != ar_call);
+              }
+              sum[mt][c] += __uint_as_float(w[i][mt][c].x);
+            }
+          arrived = __all_sync(0xffffffffu, arrived);
+        }
+      }
     }
     if (!arrived) return false;
     store_tile(sum, tile_i);
@@ -653,7 +685,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 
     // outputs and scratch may still be in use by the previous kernel until it has ended
     griddep_wait();
-    if (ar_on && ar_call == 0) ar_call = *reinterpret_cast<volatile unsigned*>(pp.ar.ws[pp.ar.rank]) + 1u;
+    if (ar_on && ar_call == 0) ar_call = *reinterpret_cast<volatile unsigned*>(pp.ar.ws[ar_rank]) + 1u;
     if (pc.kind == kWhole) {
       if (ar_on) ar_publish(fin, pc.tile);
       else store_tile(fin, pc.tile);
@@ -666,7 +698,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
           for (int c = 0; c < 4; ++c) head[mt][c] = fin[mt][c];
       } else {
-        float* dst = pp.partial + ((size_t)((cta * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
+        float* dst = sk_partial + ((size_t)((cta * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -674,14 +706,14 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
     } else {
       // tail piece: publish for the owner (the CTA that holds this tile's first chunk)
-      float* dst = pp.partial + ((size_t)((cta * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
+      float* dst = sk_partial + ((size_t)((cta * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) dst[mt * 128 + c * 32] = fin[mt][c];
       __threadfence();
       __syncwarp();
-      if (lane == 0) st_release_u32(pp.flags + cta * kConsumerWarps + warp, 1u);
+      if (lane == 0) st_release_u32(sk_flags + cta * kConsumerWarps + warp, 1u);
     }
   }
 
@@ -697,7 +729,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     for (int c0 = cta + 1; c0 <= last_cta && flags_ok; c0 += 32) {
       const int c = c0 + lane;
       if (c <= last_cta) {
-        const unsigned* f = pp.flags + c * kConsumerWarps + warp;
+        const unsigned* f = sk_flags + c * kConsumerWarps + warp;
         if (ld_acquire_u32(f) == 0u) {
           unsigned long long t0;
           asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -724,14 +756,14 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) sum[mt][cc] = head[kHeadInRegs ? mt : 0][cc];
       } else {
-        const float* own = pp.partial + ((size_t)((cta * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
+        const float* own = sk_partial + ((size_t)((cta * 2 + 1) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) sum[mt][cc] = own[mt * 128 + cc * 32];  // written by this same thread
       }
       for (int c = cta + 1; c <= last_cta; ++c) {  // fixed CTA order: deterministic
-        const float* src = pp.partial + ((size_t)((c * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
+        const float* src = sk_partial + ((size_t)((c * 2) * kConsumerWarps + warp) * MT) * 128 + lane;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -741,7 +773,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       // next launch writes them only after this grid has completed.
       __syncwarp();
       if (lane == 0)
-        for (int c = cta + 1; c <= last_cta; ++c) pp.flags[c * kConsumerWarps + warp] = 0u;
+        for (int c = cta + 1; c <= last_cta; ++c) sk_flags[c * kConsumerWarps + warp] = 0u;
       if (ar_on) {
         ar_publish(sum, head_tile);
         head_published = true;
@@ -764,10 +796,10 @@ __global__ void __launch_bounds__(kThreads, 2)
     // the call is over when every warp of the grid is through: the last CTA advances the
     // device-side call number (read by the next launch after its dependency wait)
     griddep_wait();
-    if (ar_call == 0) ar_call = *reinterpret_cast<volatile unsigned*>(pp.ar.ws[pp.ar.rank]) + 1u;
+    if (ar_call == 0) ar_call = *reinterpret_cast<volatile unsigned*>(pp.ar.ws[ar_rank]) + 1u;
     __syncwarp();
     if (lane == 0 && atom_inc_acq_rel_shared(&drained[stages]) == kConsumerWarps - 1) {
-      unsigned* hdr = reinterpret_cast<unsigned*>(pp.ar.ws[pp.ar.rank]);
+      unsigned* hdr = reinterpret_cast<unsigned*>(pp.ar.ws[ar_rank]);
       if (atomicAdd(hdr + 1, 1u) == grid - 1u) {
         hdr[1] = 0u;
         *reinterpret_cast<volatile unsigned*>(hdr) = ar_call;
@@ -781,6 +813,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 struct Launch {
   int bits, mt, zmode, group_code, src;
   int grid;
+  int cooperative;  // all CTAs must be resident together (emulated ranks wait on one another)
   size_t smem_bytes;
 };
 int launch_sk_i4(const Params& pp, const Launch& l, const CUtensorMap& tx, const CUtensorMap& ts, const CUtensorMap& tz,

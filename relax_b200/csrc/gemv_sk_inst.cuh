@@ -25,8 +25,13 @@ int launch_inst(const Params& pp, const Launch& l, const CUtensorMap& tx, const 
   cfg.dynamicSmemBytes = l.smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = launch_overlap_enabled() ? 1 : 0;
+  if (l.cooperative) {
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+  } else {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = launch_overlap_enabled() ? 1 : 0;
+  }
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   RB200_CUDA(cudaLaunchKernelEx(&cfg, kern, pp, tx, ts, tz));

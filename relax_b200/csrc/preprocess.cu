@@ -194,18 +194,20 @@ __global__ void __launch_bounds__(256) repack_ft_panel_kernel(const uint8_t* __r
       } else {
         // unit: rows g, g + 8; k = 16 t .. 16 t + 15; word j covers k4 = 4 j .. 4 j + 3 with nibble
         // slots p0 (g,k4) p4 (g,k4+1) p2 (g,k4+2) p6 (g,k4+3), p1 p5 p3 p7 the same for g + 8
-        const uint8_t* base = panel + (((bi >> 1) ^ t) << 4) + (bi & 1) * 8 + (g >> 1);
-        const int sh = (g & 1) * 4;
+        // The eight bytes at `base` of a panel row hold the tile's 16 output rows of that k: one
+        // 8-byte load (the same address for the eight lanes of a t: a broadcast) brings row g in
+        // its low word and row g + 8 in its high word, nibble g & 1 of byte g >> 1.
+        const uint8_t* base = panel + (((bi >> 1) ^ t) << 4) + (bi & 1) * 8;
+        const int sh = (g >> 1) * 8 + (g & 1) * 4;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint32_t w = 0;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint8_t* rowp = base + (t * 16 + 4 * j + kk) * kRowBytes;
-            const uint32_t lo = (((uint32_t)rowp[0] >> sh) & 15u) ^ 8u;   // row g
-            const uint32_t hi = (((uint32_t)rowp[4] >> sh) & 15u) ^ 8u;   // row g + 8
+            const uint2 v = *reinterpret_cast<const uint2*>(base + (t * 16 + 4 * j + kk) * kRowBytes);
+            const uint32_t pair = (((v.x >> sh) & 15u) | (((v.y >> sh) & 15u) << 4)) ^ 0x88u;  // rows g, g + 8
             const int slot = kk == 0 ? 0 : (kk == 1 ? 4 : (kk == 2 ? 2 : 6));
-            w |= (lo << (4 * slot)) | (hi << (4 * (slot + 1)));
+            w |= pair << (4 * slot);
           }
           words[j] = w;
         }

@@ -5,13 +5,21 @@
 // Measured on B200: one tcgen05.mma (kind::f16, M = 128, K = 16, A from tensor memory) occupies
 // the tensor pipe for 108 clocks for any N up to 192 and for 136 clocks at N = 256, so the batch
 // is the instruction's N and is made as wide as it goes (256): one instruction then does
-// 128 x 256 x 16 MACs.  (A variant with N = 192, two accumulators - epilogue overlapped with the
-// next tile's main loop - and four decode groups was measured slower, 874 against 1065 TFLOP/s:
-// every CTA streams the whole x tile from L2 for each 128-row weight tile, 148 CTAs together
-// 7-8 TB/s, and that traffic, not the tensor pipe, bounds the main loop.)  The dequantised weights are the A operand and never
-// touch shared memory: decode warps write them straight into tensor memory (tcgen05.st), the MMA
-// reads A from TMEM and B (= x) from a 128B-swizzled K-major tile in shared memory, the fp32
-// accumulator sits in 256 TMEM columns.
+// 128 x 256 x 16 MACs.  The dequantised weights are the A operand and never touch shared memory:
+// decode warps write them straight into tensor memory (tcgen05.st), the MMA reads A from TMEM and
+// B (= x) from a 128B-swizzled K-major tile in shared memory, the fp32 accumulator sits in 256
+// TMEM columns.
+//
+// What bounds it (m 2048 x k 4096 x n 22016, group 128 with zero points; timed by CUDA events):
+//  * launched back to back for a second the kernel sits on the 1000 W power cap (sw_power_cap
+//    active, SM clock 1.55-1.65 GHz): 395 us per launch; a burst of 20 launches runs 345 us.
+//  * with the MMA issuer not waiting for the decode warps (same work, no dependency) a launch
+//    takes 7 % less; without decode work at all (x stream + MMA + epilogue) 249 us, without
+//    the epilogue too 215 us.
+//  * variants measured slower in the burst: N = 192 with two accumulators (the epilogue
+//    overlapping the next tile) 874 against 1065 TFLOP/s; a pair of weight tiles per CTA against
+//    the same x stages (half the x bytes from L2) 404 us; four decode groups with eight A
+//    buffers 358 us; spinning instead of parked waits on the A hand-off 359 us.
 //
 //   warp 0 (producer)  : packed weights, one 16 KB bulk copy per (128-row tile, 4 fragment tiles)
 //   warp 1 (MMA)       : one thread, 4 x tcgen05.mma per 64-k block; commits recycle A buffers

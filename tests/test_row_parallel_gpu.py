@@ -160,3 +160,53 @@ def test_world_of_one_is_the_plain_matmul(oracle):
     C = oracle.C()
     assert_close(out.cpu().numpy(), C.epilogue(C.matmul_f32(x, C.decode_q4_nk(w, s, None, 7.0, 32))))
     assert lib.rb200_gemm_fp16_intx_allreduce(ctypes.byref(d), None, 1, 1, 8192, None) == -1
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("m,k,n,kind", [(1, 4096, 4096, "q4"), (8, 2048, 4096, "q4"), (32, 1024, 4224, "q4"),
+                                        (16, 2048, 8192, "i8")])
+def test_all_ranks_in_one_launch_on_one_gpu(oracle, world, m, k, n, kind):
+    """The exchange of the fused epilogue on a single GPU: `world` ranks inside one cooperative
+    launch (all CTAs resident together), every rank on its share of the SMs with its own
+    workspace and split-k scratch.  All ranks compute the same matmul, so every rank's block of
+    rows must be epilogue(world * (x @ wq^T)) - exact in fp32 for a power-of-two world - and the
+    blocks must agree bit for bit.  Called three times: the call number advances and the two data
+    regions alternate."""
+    lib = _lib.load()
+    x, w, s = _layer(m, k, n, kind, 7 + world)
+    rs = np.random.RandomState(world)
+    bias = rs.randn(n).astype(np.float16)
+    if kind == "q4":
+        pre = ops.preprocess_weight_q4f16(u32_to_dev(w))
+    else:
+        pre = ops.preprocess_weight_ft(to_dev(w), False)
+    sd, xd, bd = to_dev(s), to_dev(x), to_dev(bias)
+    out = torch.full((world * m, n), float("nan"), dtype=torch.float16, device="cuda")
+    nbytes = lib.rb200_gemm_allreduce_workspace_bytes(8192)
+    spaces = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in spaces])
+    d = _lib.GemmDesc()
+    d.struct_size = ctypes.sizeof(_lib.GemmDesc)
+    d.weight_bits = 4 if kind == "q4" else 8
+    d.x, d.w, d.scales, d.out, d.bias = xd.data_ptr(), pre.data_ptr(), sd.data_ptr(), out.data_ptr(), bd.data_ptr()
+    d.m, d.n, d.k, d.ldx, d.ldo = m, n, k, k, n
+    if kind == "q4":
+        d.group_size, d.scale_stride_n, d.scale_stride_g, d.zero_const = 32, k // 32, 1, 7.0
+    else:
+        d.group_size, d.scale_stride_n, d.scale_stride_g, d.zero_const = k, 1, 0, 128.0
+    for _ in range(3):
+        out.fill_(float("nan"))
+        _lib.check(lib.rb200_gemm_fp16_intx_allreduce_selftest(ctypes.byref(d), ptrs, world, 8192, None))
+        torch.cuda.synchronize()
+        st = ctypes.c_int(0)
+        assert lib.rb200_check_async_error(None, ctypes.byref(st)) == 0 and st.value == 0
+        got = out.cpu().numpy().reshape(world, m, n)
+        for r in range(1, world):
+            assert np.array_equal(got[0].view(np.uint16), got[r].view(np.uint16)), "rank %d differs from rank 0" % r
+    C = oracle.C()
+    if kind == "q4":
+        acc = C.matmul_f32(x, C.decode_q4_nk(w, s, None, 7.0, 32))
+    else:
+        acc = C.matmul_f32(x, C.decode_ft_kn(w, s, 8, -1), False)
+    exp = C.epilogue(acc * np.float32(world), bias)
+    assert_close(got[0], exp, tight=False)
