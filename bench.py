@@ -627,7 +627,7 @@ def run_gpu(args):
     done_ev = {m: torch.cuda.Event() for m in MS}
     step_ev = torch.cuda.Event()
 
-    def e2e_step(step_idx):
+    def e2e_enqueue(step_idx):
         main = torch.cuda.current_stream()
         step_ev.record(main)  # the copies of this step start after the previous step's kernels
         with torch.cuda.stream(up_stream):
@@ -642,7 +642,6 @@ def run_gpu(args):
             main.wait_event(up_ev[m])
             for name, k, n in lin:
                 bound[(s_i, name, m)]()
-                counter["launches"] += 1
                 if separate_ar is not None and name in row_parallel:
                     separate_ar(outs[(name, m)])
             done_ev[m].record(main)
@@ -650,8 +649,31 @@ def run_gpu(args):
                 down_stream.wait_event(done_ev[m])
                 a, b = o_rng[m]
                 hout[a:b].copy_(o_all[a:b], non_blocking=True)
-        down_stream.synchronize()  # the step's results are on the host
+        main.wait_stream(up_stream)
         main.wait_stream(down_stream)
+
+    # the step (copies in, 12 calls, copies out) is captured once per weight-set phase, the way a
+    # serving runtime replays its steps; without capture the same work is enqueued call by call
+    e2e_graphs = []
+    if graphs:
+        try:
+            for ph in range(WEIGHT_SETS):
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_):
+                    e2e_enqueue(ph)
+                e2e_graphs.append(g_)
+        except Exception as exc:
+            if rank == 0:
+                sys.stderr.write("end-to-end step not captured (%s); enqueueing call by call\n" % exc)
+            e2e_graphs = []
+            torch.cuda.synchronize()
+
+    def e2e_step(step_idx):
+        if e2e_graphs:
+            e2e_graphs[step_idx % WEIGHT_SETS].replay()
+        else:
+            e2e_enqueue(step_idx)
+        torch.cuda.current_stream().synchronize()  # the step's results are on the host
 
     for i in range(args.warmup):
         e2e_step(i)
@@ -798,7 +820,8 @@ def run_gpu(args):
                     "how": "per step: the 12 activations copied from pinned host memory and the 12 results copied "
                            "back, one copy per batch size each way on copy streams (a group's results travel "
                            "while the next group computes), 12 PackedFunc calls (argument arrays built once), "
-                           "sync on the last result"},
+                           "sync on the last result; " + ("the step replayed from a CUDA graph" if e2e_graphs else
+                                                          "enqueued call by call")},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
@@ -821,6 +844,7 @@ def run_gpu(args):
         # they are alive was seen to block for good after the result line had been printed.
         # Release them first, and bound the tear-down: the measurement is complete at this point.
         graphs.clear()
+        e2e_graphs.clear()
         torch.cuda.synchronize()
         import threading
         threading.Timer(20.0, lambda: os._exit(0)).start()
