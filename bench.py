@@ -825,9 +825,9 @@ def run_gpu(args):
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
-                         # DRAM bytes per launch: the ncu capture of the gate_up M=1 launch read+wrote
-                         # 1.0016 x its algorithmic bytes; scaled to the mean launch
-                         "traffic": 1.0016 * sum(c for _, c in per_shape.values()) / len(per_shape),
+                         # DRAM bytes per launch: the ncu capture of the gate_up M=1 launch read + wrote
+                         # 50.84 MB for 50.78 MB of algorithmic bytes (x 1.0012); scaled to the mean launch
+                         "traffic": 1.0012 * sum(c for _, c in per_shape.values()) / len(per_shape),
                          "traffic_source": "profiles/gemv_sk_kernel_gate_up_m1.md, scaled by algorithmic bytes",
                          "peak_kind": peak_kind,
                          "kernel": "gemv_sk_kernel",
