@@ -214,9 +214,10 @@ def _events():
     return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
 
-def graph_time(fn, calls=8, reps=3, allow_graph=True):
+def graph_time(fn, calls=8, reps=3, allow_graph=True, how=None):
     """ms per call of `fn`: `calls` back-to-back calls captured in a CUDA graph (so that no host time
-    is in the figure), `reps` replays between two events; eager launches when capture is refused."""
+    is in the figure), `reps` replays between two events; eager launches when capture is refused.
+    `how` (a dict) receives which of the two it was."""
     import torch
     fn()
     torch.cuda.synchronize()
@@ -231,6 +232,8 @@ def graph_time(fn, calls=8, reps=3, allow_graph=True):
         except Exception:
             g_ = None
         torch.cuda.synchronize()
+    if how is not None:
+        how["mode"] = "cuda graph replay" if g_ is not None else "eager launches"
     a_, b_ = _events()
     a_.record()
     for _ in range(reps):
@@ -379,27 +382,34 @@ def mixtral_block(world, rank, dev, barrier):
     x = torch.randn((T, H), device=dev, generator=g).half()
     y1 = torch.empty((2 * T, F), dtype=torch.float16, device=dev)
     y2 = torch.zeros((2 * T, H), dtype=torch.float16, device=dev)
-    holder = {}
+    # every buffer of the layer exists before the first call: nothing allocates inside it, so the
+    # layer can be captured in a CUDA graph
+    route = (torch.empty(E, dtype=torch.int64, device=dev), torch.empty(2 * T, dtype=torch.int32, device=dev),
+             torch.empty(2 * T, dtype=torch.float32, device=dev), torch.empty(2 * T, dtype=torch.int32, device=dev))
+    route_ws = torch.empty(ops.moe_route_workspace_bytes(T, 2), dtype=torch.uint8, device=dev)
+    xg = torch.empty((2 * T, H), dtype=torch.float16, device=dev)
+    res = torch.empty((T, H), dtype=torch.float16, device=dev)
+    holder = {"res": res, "route": route}
 
     def layer():
-        indptr, tok, gate, rof = ops.moe_route(logits, 2)
-        xg = ops.moe_gather(x, tok)
+        indptr, tok, gate, rof = ops.moe_route(logits, 2, out=route, workspace=route_ws)
+        ops.moe_gather(x, tok, out=xg)
         ops.moe_gemm_ft(xg, w1, s1, indptr, out=y1, first_expert=e0)
         if world > 1:
             y2.zero_()  # rows of the other ranks' experts contribute nothing to this rank's partial sum
         ops.moe_gemm_ft(y1, w2, s2, indptr, out=y2, first_expert=e0)
-        res = ops.moe_combine(y2, rof, gate, 2)
+        ops.moe_combine(y2, rof, gate, 2, out=res)
         if world > 1:
             dist.all_reduce(res)
-        holder["res"], holder["route"] = res, (indptr, tok, gate, rof)
 
     layer()
     torch.cuda.synchronize()
     barrier()
-    t = max_over_ranks(graph_time(layer, calls=4, allow_graph=False), world, dev)
+    how = {}
+    t = max_over_ranks(graph_time(layer, calls=4, how=how), world, dev)
     flops = 2.0 * 2 * T * H * F * 2
     entry = {"us": t * 1e3, "tflops_total": flops / (t * 1e-3) / 1e12, "experts_per_rank": e1 - e0,
-             "timed_with": "eager launches (the routing step allocates its outputs)",
+             "timed_with": how.get("mode", "eager launches"),
              "allreduce": "nccl [512, 4096] fp16" if world > 1 else "none"}
     # parity: a few tokens against the oracle (their two experts regenerated on rank 0)
     layer()

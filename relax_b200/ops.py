@@ -186,44 +186,60 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-def moe_route(logits: torch.Tensor, top_k: int):
+def moe_route(logits: torch.Tensor, top_k: int, out=None, workspace: Optional[torch.Tensor] = None):
     """Softmax + top-k routing (``rb200_moe_route``): returns ``(indptr int64 [E], token_of_row int32
     [R], gate_of_row fp32 [R], row_of_flat int32 [R])`` with rows sorted by expert, the convention
-    of the grouped matmul (src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64)."""
+    of the grouped matmul (src/runtime/contrib/cutlass/fp16_group_gemm.cu:39-64).  ``out`` (the same
+    four tensors) and ``workspace`` (uint8, :func:`moe_route_workspace_bytes`) make the call
+    allocation-free, e.g. for CUDA-graph capture; ``logits`` must then be contiguous fp32."""
     import ctypes
     from . import _lib
     lib = _lib.load()
     t, e = logits.shape
     r = t * top_k
     dev = logits.device
-    indptr = torch.empty(e, dtype=torch.int64, device=dev)
-    token_of_row = torch.empty(r, dtype=torch.int32, device=dev)
-    gate_of_row = torch.empty(r, dtype=torch.float32, device=dev)
-    row_of_flat = torch.empty(r, dtype=torch.int32, device=dev)
+    if out is None:
+        out = (torch.empty(e, dtype=torch.int64, device=dev), torch.empty(r, dtype=torch.int32, device=dev),
+               torch.empty(r, dtype=torch.float32, device=dev), torch.empty(r, dtype=torch.int32, device=dev))
+    indptr, token_of_row, gate_of_row, row_of_flat = out
     nbytes = lib.rb200_moe_route_workspace_bytes(t, top_k)
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-    logits = logits.contiguous().float()
+    if workspace is None:
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    elif workspace.numel() < nbytes:
+        raise ValueError("routing workspace holds %d bytes, %d needed" % (workspace.numel(), nbytes))
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        logits = logits.contiguous().float()
     _lib.check(lib.rb200_moe_route(_ptr(logits), t, e, top_k, _ptr(indptr), _ptr(token_of_row), _ptr(gate_of_row),
-                                   _ptr(row_of_flat), _ptr(ws), nbytes,
+                                   _ptr(row_of_flat), _ptr(workspace), workspace.numel(),
                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return indptr, token_of_row, gate_of_row, row_of_flat
 
 
-def moe_gather(x: torch.Tensor, token_of_row: torch.Tensor) -> torch.Tensor:
+def moe_route_workspace_bytes(tokens: int, top_k: int) -> int:
+    from . import _lib
+    return int(_lib.load().rb200_moe_route_workspace_bytes(tokens, top_k))
+
+
+def moe_gather(x: torch.Tensor, token_of_row: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[r] = x[token_of_row[r]]``: the rows of x in the grouped matmul's order."""
     import ctypes
     from . import _lib
-    out = torch.empty(token_of_row.numel(), x.shape[1], dtype=torch.float16, device=x.device)
+    if out is None:
+        out = torch.empty(token_of_row.numel(), x.shape[1], dtype=torch.float16, device=x.device)
     x = x.contiguous()
     _lib.check(_lib.load().rb200_moe_gather(_ptr(x), _ptr(token_of_row), _ptr(out), token_of_row.numel(), x.shape[1],
                                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out
 
 
-def moe_combine(y: torch.Tensor, row_of_flat: torch.Tensor, gate_of_row: torch.Tensor, top_k: int) -> torch.Tensor:
+def moe_combine(y: torch.Tensor, row_of_flat: torch.Tensor, gate_of_row: torch.Tensor, top_k: int,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = sum over the token's top_k rows of gate * y[row]`` (fp32 sum, one rounding)."""
     import ctypes
     from . import _lib
     tokens = row_of_flat.numel() // top_k
-    out = torch.empty(tokens, y.shape[1], dtype=torch.float16, device=y.device)
+    if out is None:
+        out = torch.empty(tokens, y.shape[1], dtype=torch.float16, device=y.device)
     y = y.contiguous()
     _lib.check(_lib.load().rb200_moe_combine(_ptr(y), _ptr(row_of_flat), _ptr(gate_of_row), _ptr(out), tokens, top_k,
                                              y.shape[1], ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))

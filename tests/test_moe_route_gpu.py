@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from relax_b200 import ops
+from tests.test_gemv_gpu import _check_status
 from tests.util import assert_close, to_dev
 
 pytestmark = pytest.mark.gpu
@@ -74,3 +75,46 @@ def test_expert_layer_end_to_end(oracle):
     for j in range(top_k):
         acc = acc + e_gate[rof[:, j]][:, None] * y_ref[rof[:, j]]
     assert_close(out.cpu().numpy(), acc.astype(np.float16), tight=False)
+
+
+def test_expert_layer_with_caller_buffers_replays_from_a_graph():
+    """The same layer with every output and the routing workspace supplied by the caller: nothing
+    allocates inside it, so it can be captured once and replayed; the replay on new logits and
+    activations must equal the eager, allocating form bit for bit."""
+    g = np.random.Generator(np.random.PCG64(12))
+    tokens, experts, top_k, k, n, group = 64, 8, 2, 256, 256, 128
+    w = g.integers(-128, 128, size=(experts, k, n // 2), dtype=np.int8)
+    scales = g.uniform(0.001, 0.01, size=(experts, k // group, n)).astype(np.float16)
+    pre, sd = ops.preprocess_weight_ft(to_dev(w), True), to_dev(scales)
+    logits = torch.zeros((tokens, experts), dtype=torch.float32, device="cuda")
+    x = torch.zeros((tokens, k), dtype=torch.float16, device="cuda")
+    rows = tokens * top_k
+    route = (torch.empty(experts, dtype=torch.int64, device="cuda"), torch.empty(rows, dtype=torch.int32, device="cuda"),
+             torch.empty(rows, dtype=torch.float32, device="cuda"), torch.empty(rows, dtype=torch.int32, device="cuda"))
+    ws = torch.empty(ops.moe_route_workspace_bytes(tokens, top_k), dtype=torch.uint8, device="cuda")
+    xg = torch.empty((rows, k), dtype=torch.float16, device="cuda")
+    y = torch.empty((rows, n), dtype=torch.float16, device="cuda")
+    out = torch.empty((tokens, n), dtype=torch.float16, device="cuda")
+
+    def layer():
+        indptr, tok, gate, rof = ops.moe_route(logits, top_k, out=route, workspace=ws)
+        ops.moe_gather(x, tok, out=xg)
+        ops.moe_gemm_ft(xg, pre, sd, indptr, out=y)
+        ops.moe_combine(y, rof, gate, top_k, out=out)
+
+    layer()  # first call outside the capture (library scratch)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer()
+    for seed in (1, 2):
+        gg = np.random.Generator(np.random.PCG64(100 + seed))
+        logits.copy_(to_dev(gg.standard_normal((tokens, experts), dtype=np.float32)))
+        x.copy_(to_dev(gg.standard_normal((tokens, k), dtype=np.float32).astype(np.float16)))
+        graph.replay()
+        torch.cuda.synchronize()
+        indptr, tok, gate, rof = ops.moe_route(logits, top_k)
+        exp = ops.moe_combine(ops.moe_gemm_ft(ops.moe_gather(x, tok), pre, sd, indptr), rof, gate, top_k)
+        torch.cuda.synchronize()
+        assert torch.equal(out, exp)
+    _check_status()
