@@ -468,48 +468,36 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
       for (int c = 0; c < 4; ++c) sum[mt][c] = 0.0f;
     bool arrived = true;
-    // the words of several ranks are requested together (as many as the register file takes),
-    // so that the sum over eight ranks costs two to four memory round trips, not eight
-    constexpr int kRanksPerBatch = 8 / MT;
-    for (int r0 = 0; r0 < pp.ar.world && arrived; r0 += kRanksPerBatch) {
-      uint2 w[kRanksPerBatch][MT][4];
+    // one rank after the other: requesting the words of several ranks together before looking at
+    // any of them measured slower (272 against 262 us per step at four ranks)
+    for (int r = 0; r < pp.ar.world && arrived; ++r) {
+      const uint2* src = ar_slot(ar_rank, ar_call, r, blk) + lane;
+      uint2 w[MT][4];
 #pragma unroll
-      for (int i = 0; i < kRanksPerBatch; ++i) {
-        if (r0 + i < pp.ar.world) {
-          const uint2* src = ar_slot(ar_rank, ar_call, r0 + i, blk) + lane;
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
+        for (int c = 0; c < 4; ++c) w[mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) w[i][mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
-        }
-      }
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int i = 0; i < kRanksPerBatch; ++i) {
-        if (r0 + i < pp.ar.world && arrived) {
-          const uint2* src = ar_slot(ar_rank, ar_call, r0 + i, blk) + lane;
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              if (arrived && w[i][mt][c].y != ar_call) {  // not there yet: poll this word
-                unsigned long long t0;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-                do {
-                  w[i][mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
-                  unsigned long long t1;
-                  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                  if (t1 - t0 > limit_ns) {
-                    if (p.status) atomicExch(p.status, kStatusWaitTimeout);
-                    arrived = false;
-                    break;
-                  }
-                } while (w[i][mt][c].y != ar_call);
+        for (int c = 0; c < 4; ++c) {
+          if (arrived && w[mt][c].y != ar_call) {  // not there yet: poll this word
+            unsigned long long t0;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+            do {
+              w[mt][c] = ld_volatile_v2(src + (mt * 4 + c) * 32);
+              unsigned long long t1;
+              asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+              if (t1 - t0 > limit_ns) {
+                if (p.status) atomicExch(p.status, kStatusWaitTimeout);
+                arrived = false;
+                break;
               }
-              sum[mt][c] += __uint_as_float(w[i][mt][c].x);
-            }
-          arrived = __all_sync(0xffffffffu, arrived);
+            } while (w[mt][c].y != ar_call);
+          }
+          sum[mt][c] += __uint_as_float(w[mt][c].x);
         }
-      }
+      arrived = __all_sync(0xffffffffu, arrived);
     }
     if (!arrived) return false;
     store_tile(sum, tile_i);
