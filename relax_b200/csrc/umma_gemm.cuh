@@ -616,16 +616,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         reduce_here = s_last[grp] != 0;
         if (reduce_here) __threadfence();
       }
-      // the accumulator columns of step i + 1 are requested before step i is worked on
-      uint32_t r_next[16];
-      if (reduce_here && c_begin < c_end && m0 + c_begin < m_end) ug::tc_ld16_issue(lane_taddr | (d_col0 + c_begin), r_next);
       for (int c0 = c_begin; reduce_here && c0 < c_end; c0 += 16, ++estep) {
         if (m0 + c0 >= m_end) break;
         float v[16];
-        ug::tc_ld16_wait(r_next);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r_next[i]);
-        if (c0 + 16 < c_end && m0 + c0 + 16 < m_end) ug::tc_ld16_issue(lane_taddr | (d_col0 + c0 + 16), r_next);
+        tc_ld16(lane_taddr | (d_col0 + c0), v);
         if (SPLITK && S > 1) {
           // all splits in split order, this CTA's own part straight from tensor memory
           float acc[16];
