@@ -19,7 +19,9 @@
 //  * variants measured slower in the burst: N = 192 with two accumulators (the epilogue
 //    overlapping the next tile) 874 against 1065 TFLOP/s; a pair of weight tiles per CTA against
 //    the same x stages (half the x bytes from L2) 404 us; four decode groups with eight A
-//    buffers 358 us; spinning instead of parked waits on the A hand-off 359 us.
+//    buffers 358 us; spinning instead of parked waits on the A hand-off 359 us; requesting the
+//    accumulator columns of the next epilogue step before working on the current one 345 us
+//    (no change).
 //
 //   warp 0 (producer)  : packed weights, one 16 KB bulk copy per (128-row tile, 4 fragment tiles)
 //   warp 1 (MMA)       : one thread, 4 x tcgen05.mma per 64-k block; commits recycle A buffers
