@@ -34,9 +34,14 @@ static int run_common(const GemvParams& p_in, int bits, int zmode, int sm_count,
   pp.w_expert_bytes = w_expert_bytes;
   pp.s_expert_stride = s_expert_stride;
   if (grouped) {
-    // the split of the rows is known only on the device: tiles as wide as the MMA allows, since
-    // one tcgen05.mma costs the same for 32 batch rows as for 256
-    pp.nb = p.m >= kMaxNb ? kMaxNb : (p.m + 31) / 32 * 32;
+    // The split of the rows is known only on the device.  One tcgen05.mma occupies the tensor
+    // pipe for the same time at any N up to 192 and 26 % longer at 256, so the tile is as wide
+    // as an expert's share is likely to be: 128 or 192 batch rows when the rows, spread evenly
+    // over the experts, stay well inside that (an expert above the width takes a second tile),
+    // 256 otherwise.
+    const long long even = p.m / num_experts;
+    if (p.m < kMaxNb) pp.nb = (p.m + 31) / 32 * 32;
+    else pp.nb = even <= 96 ? 128 : (even <= 160 ? 192 : kMaxNb);
   } else {
     // balanced batch tiles of at most 256 rows, padded to the 32 rows the epilogue split needs
     const int m_tiles = (p.m + kMaxNb - 1) / kMaxNb;
