@@ -211,8 +211,7 @@ int rb200_allreduce_oneshot(void* const* workspaces, int rank, int world, const 
   p.region_bytes = region_bytes_for(max_count);
   p.status = sc->status;
   p.wait_limit_ns = (wait_limit_ms() ? (unsigned long long)wait_limit_ms() : 2000ull) * 1000000ull;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid_for(count), 1, 1);
   cfg.blockDim = dim3(kArThreads, 1, 1);
   cfg.stream = static_cast<cudaStream_t>(stream);

@@ -32,8 +32,7 @@ int launch_inst(ClusterParams cp, const ClusterLaunch& l, const CUtensorMap& ts,
   if (stages < 1) stages = 1;
   const size_t smem = smem_for(l, stages);
 
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
