@@ -56,12 +56,27 @@ __global__ void repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restri
   const int64_t expert_bytes = K * N * BITS / 8;
   for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total_units;
        u += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t e = u / units_per_expert;
-    const int64_t r = u % units_per_expert;
-    const int lane = (int)(r & 31);
-    const int64_t tile = r >> 5;
+    // unit index -> (expert, row block, k block, lane): 32-bit divisions whenever the unit count
+    // fits (64-bit ones are routines of a hundred instructions, three per 16 bytes moved)
+    int64_t e, nb, kb;
+    int lane;
     const int64_t KB = K / kFrag;
-    const int64_t nb = tile / KB, kb = tile % KB;
+    if (total_units < (1ll << 31)) {
+      const uint32_t u32 = (uint32_t)u, upe = (uint32_t)units_per_expert, kb32 = (uint32_t)KB;
+      const uint32_t e32 = u32 / upe, r32 = u32 - e32 * upe;
+      const uint32_t tile = r32 >> 5, nb32 = tile / kb32;
+      e = e32;
+      lane = (int)(r32 & 31u);
+      nb = nb32;
+      kb = tile - nb32 * kb32;
+    } else {
+      e = u / units_per_expert;
+      const int64_t r = u % units_per_expert;
+      lane = (int)(r & 31);
+      const int64_t tile = r >> 5;
+      nb = tile / KB;
+      kb = tile % KB;
+    }
     const int g = lane >> 2, t = lane & 3;
     const uint8_t* s = src + e * expert_bytes;
     uint32_t words[4];
