@@ -238,6 +238,9 @@ RB200_API int rb200_gemm_fp16_intx_noalloc(const rb200_gemm_desc* desc, void* st
  * - an extension: the reference has no quantised grouped GEMM.
  * Needs n % 128 == 0, k % 64 == 0, 16-byte aligned x / out rows, num_experts <= 64.
  * workspace is accepted for signature parity and not used (nothing is allocated per call).
+ * Packed weights with at most 32 rows in all (decode-size batches) run as one launch of the
+ * decode kernel per expert - each launch reads its row range from indptr on the device and
+ * returns at once when the expert has no rows - and then need only n % 16 == 0.
  */
 typedef struct rb200_group_gemm_desc {
   uint32_t struct_size;   /* sizeof(rb200_group_gemm_desc) */
